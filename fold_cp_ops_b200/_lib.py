@@ -1,0 +1,120 @@
+"""ctypes binding of ``libtrimul_sm100.so`` (C ABI declared in ``include/trimul_sm100.h``).
+
+There is exactly one compute path: the hand-written sm_100a kernels in that library.  If the
+library is missing or the device is not compute capability 10.x the functions here raise; nothing
+falls back to PyTorch or to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_NAME = "libtrimul_sm100.so"
+
+TRIMUL_OK = 0
+ERR_INVALID_ARGUMENT = -1
+ERR_UNSUPPORTED_ARCH = -2
+ERR_CUDA = -3
+ERR_UNSUPPORTED_SHAPE = -4
+
+MASK_NONE, MASK_BF16, MASK_FP32, MASK_U8 = 0, 1, 2, 3
+OUTGOING, INCOMING = 0, 1
+MAX_PEERS = 8
+
+#: every symbol include/trimul_sm100.h declares; the CPU test-suite checks the library exports them
+EXPORTED_SYMBOLS = (
+    "trimul_sm100_query",
+    "trimul_sm100_workspace",
+    "trimul_sm100_last_error",
+    "trimul_sm100_pack_weights",
+    "trimul_sm100_ln_gated_proj",
+    "trimul_sm100_tri_contract",
+    "trimul_sm100_ln_out_proj",
+    "trimul_sm100_forward",
+    "trimul_sm100_peer_signal",
+    "trimul_sm100_peer_wait",
+)
+
+
+class Caps(C.Structure):
+    _fields_ = [("cc_major", C.c_int32), ("cc_minor", C.c_int32), ("num_sms", C.c_int32),
+                ("max_smem_per_block", C.c_int32), ("supported", C.c_int32)]
+
+
+class Geom(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("n", C.c_int32), ("d", C.c_int32), ("cp0", C.c_int32),
+                ("cp1", C.c_int32), ("rank", C.c_int32), ("direction", C.c_int32), ("eps", C.c_float)]
+
+
+class Workspace(C.Structure):
+    _fields_ = [("ab_bytes", C.c_uint64), ("tri_bytes", C.c_uint64), ("gate_bytes", C.c_uint64)]
+
+
+class TrimulLibraryError(RuntimeError):
+    """The native library is missing, cannot be loaded, or a call into it failed."""
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def library_path() -> Path:
+    override = os.environ.get("CPO_TRIMUL_LIB")
+    return Path(override) if override else _PKG_DIR / LIB_NAME
+
+
+def load():
+    """Load the shared library once; raise :class:`TrimulLibraryError` if it is not there."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.exists():
+            raise TrimulLibraryError(
+                f"{path} not found. Build it with `python -m fold_cp_ops_b200.build` (needs nvcc); "
+                "there is no PyTorch or CPU fallback for the TriMul kernels."
+            )
+        try:
+            lib = C.CDLL(str(path))
+        except OSError as exc:  # pragma: no cover - depends on the host
+            raise TrimulLibraryError(f"cannot load {path}: {exc}") from exc
+        vp, i32, u64, f32p = C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p
+        lib.trimul_sm100_last_error.restype = C.c_char_p
+        lib.trimul_sm100_last_error.argtypes = []
+        lib.trimul_sm100_query.argtypes = [C.c_int, C.POINTER(Caps)]
+        lib.trimul_sm100_workspace.argtypes = [C.POINTER(Geom), C.POINTER(Workspace)]
+        lib.trimul_sm100_pack_weights.argtypes = [i32, vp, vp, vp, f32p, f32p, f32p, vp, f32p, vp]
+        lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p,
+                                                   C.POINTER(vp), vp, vp, u64, vp]
+        lib.trimul_sm100_tri_contract.argtypes = [C.POINTER(Geom), vp, C.POINTER(vp), vp, u64, vp]
+        lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, f32p, f32p, vp, f32p, vp, vp, u64, vp]
+        lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, f32p, f32p,
+                                             vp, f32p, vp, vp, vp, vp, vp, u64, vp]
+        if hasattr(lib, "trimul_sm100_peer_signal"):
+            lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, i32, u64, vp]
+            lib.trimul_sm100_peer_wait.argtypes = [vp, i32, i32, u64, vp, u64, vp]
+        for name in ("trimul_sm100_query", "trimul_sm100_workspace", "trimul_sm100_pack_weights",
+                     "trimul_sm100_ln_gated_proj", "trimul_sm100_tri_contract", "trimul_sm100_ln_out_proj",
+                     "trimul_sm100_forward"):
+            getattr(lib, name).restype = C.c_int
+        _lib = lib
+        return lib
+
+
+def last_error() -> str:
+    return load().trimul_sm100_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int, what: str) -> None:
+    if rc == TRIMUL_OK:
+        return
+    msg = last_error()
+    if rc == ERR_UNSUPPORTED_SHAPE or rc == ERR_INVALID_ARGUMENT:
+        raise ValueError(f"{what}: {msg}")
+    raise TrimulLibraryError(f"{what} failed (code {rc}): {msg}")

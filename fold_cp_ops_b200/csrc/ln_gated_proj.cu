@@ -1,0 +1,433 @@
+// Input LayerNorm fused into the gated dual projection:
+//     xn   = LayerNorm(x) * gamma + beta                         (fp32 statistics, bf16 operand)
+//     a|b  = (xn Wp^T + bp) * sigmoid(xn Wg^T + bg) * mask       (2D channels, bf16)
+//     gate = sigmoid(xn Wo^T + bo)                               (D channels, bf16, stays local)
+// (Reference: ops 1-5 and 10 of trimul_ref, fold_cp_ops/workflows/trimul_autotune.py:1505-1524;
+//  front kernel fold_cp_ops/distributed/dual_gated_gemm_a2a.py:56-76; K1 kernels/layernorm.py:730.)
+//
+// Persistent CTA, 128-token tiles.  Eight LayerNorm warps pull token rows from HBM into
+// registers, normalise, and write the bf16 operand tile into shared memory in the K-major
+// 128-byte-swizzle layout the tensor core reads; weights stream through a TMA ring (they live in
+// L2); one thread issues tcgen05.mma for five N=D column chunks per tile into two TMEM
+// accumulators; eight epilogue warps apply bias / sigmoid gate / mask and store each channel's
+// 128 tokens contiguously into the channel-major operand plane of the rank that owns the channel
+// (front all-to-all fused in the store; at cp=1 that rank is this GPU).
+#include "trimul_common.cuh"
+#include "trimul_kernels.h"
+
+namespace trimul {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int kThreads = 640;       // w0 TMA, w1 MMA, w2 TMEM alloc, w3 idle, w4-11 epilogue, w12-19 LayerNorm
+constexpr int kEpiWarp0 = 4;
+constexpr int kLnWarp0 = 12;
+constexpr int kNumChunks = 5;       // a_lo, a_hi, b_lo, b_hi, gate
+
+template <int D>
+struct Cfg {
+  static constexpr int CH = D / 2;              // channels per gated chunk
+  static constexpr int KB = D / 64;             // 64-wide K blocks
+  static constexpr int kABytes = BM * D * 2;    // one operand tile
+  static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
+  static constexpr int kWStageBytes = D * 128;  // D weight rows x 64 k
+  static constexpr int kWStages = (D == 256) ? 3 : 4;
+  static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
+  static constexpr int kTileBytes = 2 * kABytes + kWStages * kWStageBytes;
+};
+
+template <int D>
+struct SmemCtl {
+  uint64_t w_full[Cfg<D>::kWStages];
+  uint64_t w_empty[Cfg<D>::kWStages];
+  uint64_t xn_ready[2];
+  uint64_t x_empty[2];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  volatile uint32_t armed[Cfg<D>::kWStages];
+};
+
+template <int D>
+constexpr int smem_bytes() {
+  return Cfg<D>::kTileBytes + 1024 + 256;
+}
+
+__device__ __forceinline__ float sigmoid_tanh(float x) {
+  // sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5 : one MUFU op instead of two
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+struct TileCoord {
+  int b, line, w0;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(long t, int tiles_per_line, int n_lines) {
+  const long lines = t / tiles_per_line;
+  TileCoord c;
+  c.w0 = static_cast<int>(t - lines * tiles_per_line) * BM;
+  c.b = static_cast<int>(lines / n_lines);
+  c.line = static_cast<int>(lines - static_cast<long>(c.b) * n_lines);
+  return c;
+}
+
+}  // namespace
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* a_tiles = tiles;                       // 2 x kABytes
+  uint8_t* w_tiles = tiles + 2 * C::kABytes;      // kWStages x kWStageBytes
+  SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_per_line = (p.n_walk + BM - 1) / BM;
+  const long total_tiles = static_cast<long>(p.batch) * p.n_lines * tiles_per_line;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kWStages; ++s) {
+      sm100::mbar_init(&ctl->w_full[s], 1);
+      sm100::mbar_init(&ctl->w_empty[s], 1);
+      ctl->armed[s] = 2;
+    }
+    for (int a = 0; a < 2; ++a) {
+      sm100::mbar_init(&ctl->xn_ready[a], 8);    // one arrive per LayerNorm warp
+      sm100::mbar_init(&ctl->x_empty[a], 1);     // tcgen05.commit
+      sm100::mbar_init(&ctl->tmem_full[a], 1);   // tcgen05.commit
+      sm100::mbar_init(&ctl->tmem_empty[a], 8);  // one arrive per epilogue warp
+    }
+    ctl->abort_flag = 0;
+    sm100::mbar_init_fence();
+  }
+  if (warp == 2) {
+    sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tcgen05_fence_before_sync();
+  __syncthreads();
+  sm100::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const uint64_t tmo = p.timeout_ns;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ weight producer (TMA from L2)
+    if (lane == 0) {
+      sm100::tma_prefetch_desc(&tmW);
+      PipeState ps{0, 0};
+      bool ok = true;
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int c = 0; c < kNumChunks && ok; ++c) {
+          for (int kb = 0; kb < C::KB; ++kb) {
+            if (!sm100::mbar_wait(&ctl->w_empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
+              report_timeout(p.status, kKernelGatedProj, 0, c * 16 + kb);
+              ok = false;
+              break;
+            }
+            ctl->armed[ps.stage] = ps.phase;
+            sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], C::kWStageBytes);
+            sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes, &tmW, &ctl->w_full[ps.stage], kb * 64, c * D);
+            ps.advance(C::kWStages);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
+      PipeState ps{0, 0};
+      uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
+      bool ok = true;
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!sm100::mbar_wait(&ctl->xn_ready[buf], buf_phase, abort_flag, tmo)) {
+          report_timeout(p.status, kKernelGatedProj, 1, -1);
+          break;
+        }
+        sm100::tcgen05_fence_after_sync();
+        const uint32_t a_addr = sm100::smem_u32(a_tiles + buf * C::kABytes);
+        for (int c = 0; c < kNumChunks && ok; ++c) {
+          if (!sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelGatedProj, 1, -2);
+            ok = false;
+            break;
+          }
+          sm100::tcgen05_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + acc * D;
+          for (int kb = 0; kb < C::KB; ++kb) {
+            if (!sm100::mbar_wait(&ctl->w_full[ps.stage], ps.phase, abort_flag, tmo)) {
+              report_timeout(p.status, kKernelGatedProj, 1, c * 16 + kb);
+              ok = false;
+              break;
+            }
+            sm100::tcgen05_fence_after_sync();
+            const uint64_t da = sm100::umma_desc_kmajor_sw128(a_addr + kb * C::kKBlockBytes);
+            const uint64_t db = sm100::umma_desc_kmajor_sw128(sm100::smem_u32(w_tiles + ps.stage * C::kWStageBytes));
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+            }
+            sm100::umma_commit(&ctl->w_empty[ps.stage]);
+            ps.advance(C::kWStages);
+          }
+          if (!ok) break;
+          sm100::umma_commit(&ctl->tmem_full[acc]);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        sm100::umma_commit(&ctl->x_empty[buf]);  // operand tile free once every MMA of the tile retired
+        if (++buf == 2) {
+          buf = 0;
+          buf_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp >= kLnWarp0) {
+    // ------------------------------------------------------------ LayerNorm prologue (8 warps)
+    constexpr int CPR = D / 8;        // 16-byte chunks per row
+    constexpr int RPP = 32 / CPR;     // rows one warp-wide load covers
+    constexpr int ROWS_PER_WARP = 16;
+    constexpr int BATCH_ROWS = 8;     // rows in flight per warp
+    constexpr int PASSES = BATCH_ROWS / RPP;
+    const int lw = warp - kLnWarp0;
+    const int chunk = lane % CPR;
+    const int sub = lane / CPR;
+    float gam[8], bet[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      gam[e] = p.ln_w[chunk * 8 + e];
+      bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
+    }
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    uint32_t buf = 0, buf_phase = 0;
+    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
+      const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+      bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
+        break;
+      }
+      uint8_t* a_tile = a_tiles + buf * C::kABytes;
+#pragma unroll 1
+      for (int half = 0; half < ROWS_PER_WARP / BATCH_ROWS; ++half) {
+        uint4 raw[PASSES];
+#pragma unroll
+        for (int ps = 0; ps < PASSES; ++ps) {
+          const int r = lw * ROWS_PER_WARP + half * BATCH_ROWS + ps * RPP + sub;
+          const int w = tc.w0 + r;
+          if (w < p.n_walk) {
+            raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
+          } else {
+            raw[ps] = make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int ps = 0; ps < PASSES; ++ps) {
+          const int r = lw * ROWS_PER_WARP + half * BATCH_ROWS + ps * RPP + sub;
+          float v[8];
+          v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
+          v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
+          v[4] = sm100::bf16_lo(raw[ps].z); v[5] = sm100::bf16_hi(raw[ps].z);
+          v[6] = sm100::bf16_lo(raw[ps].w); v[7] = sm100::bf16_hi(raw[ps].w);
+          float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+#pragma unroll
+          for (int o = CPR / 2; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          const float mean = s * (1.0f / D);
+          float q = 0.0f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[e] -= mean;
+            q = fmaf(v[e], v[e], q);
+          }
+#pragma unroll
+          for (int o = CPR / 2; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+          const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
+          uint4 o4;
+          o4.x = sm100::pack_bf16x2(fmaf(v[0] * rstd, gam[0], bet[0]), fmaf(v[1] * rstd, gam[1], bet[1]));
+          o4.y = sm100::pack_bf16x2(fmaf(v[2] * rstd, gam[2], bet[2]), fmaf(v[3] * rstd, gam[3], bet[3]));
+          o4.z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
+          o4.w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
+          // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
+          const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(a_tile + off) = o4;
+        }
+      }
+      sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
+      if (++buf == 2) {
+        buf = 0;
+        buf_phase ^= 1;
+      }
+    }
+  } else if (warp >= kEpiWarp0) {
+    // ------------------------------------------------------------ epilogue (8 warps)
+    const int quarter = warp & 3;
+    const int hh = (warp - kEpiWarp0) >> 2;  // which half of the chunk's columns
+    const int r = quarter * 32 + lane;
+    const int d_loc_mask = (1 << p.d_loc_log2) - 1;
+    const int d_loc_n = 1 << p.d_loc_log2;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
+      const int w = tc.w0 + r;
+      const bool valid = w < p.n_walk;
+      const long srow = tc.b * p.batch_rows + tc.line * p.line_rows + static_cast<long>(w) * p.walk_rows;
+      float mval = 1.0f;
+      if (valid && p.mask_kind != 0) {
+        if (p.mask_kind == 1) {
+          mval = __bfloat162float(static_cast<const __nv_bfloat16*>(p.mask)[srow]);
+        } else if (p.mask_kind == 2) {
+          mval = static_cast<const float*>(p.mask)[srow];
+        } else {
+          mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
+        }
+      }
+      const long dst_tok = p.dst_base + tc.line * p.dst_line + w;
+      for (int c = 0; c < kNumChunks; ++c) {
+        ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          report_timeout(p.status, kKernelGatedProj, 2, c);
+          break;
+        }
+        sm100::tcgen05_fence_after_sync();
+        const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
+        if (c < 4) {
+          // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
+          const int h = c >> 1;
+          constexpr int GROUPS = C::CH / 2 / 32;
+#pragma unroll 1
+          for (int g = 0; g < GROUPS; ++g) {
+            const int col0 = hh * (C::CH / 2) + g * 32;
+            uint32_t pv[32], gv[32];
+            sm100::tmem_ld_32x32b_x32(trow + col0, pv);
+            sm100::tmem_ld_32x32b_x32(trow + C::CH + col0, gv);
+            sm100::tmem_ld_wait();
+            if (valid) {
+              const float* bias_p = p.bias + c * D + col0;
+              const float* bias_g = bias_p + C::CH;
+              const int d0 = (c & 1) * C::CH + col0;  // channel inside the a (or b) half
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const float pr = __uint_as_float(pv[e]) + __ldg(bias_p + e);
+                const float ga = __uint_as_float(gv[e]) + __ldg(bias_g + e);
+                const float val = pr * sigmoid_tanh(ga) * mval;
+                const int d = d0 + e;
+                const int owner = d >> p.d_loc_log2;
+                const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[owner]);
+                dst[plane * p.plane_elems + dst_tok] = __float2bfloat16_rn(val);
+              }
+            }
+          }
+        } else {
+          // output-gate chunk: sigmoid only, token-major local store
+          constexpr int GROUPS = D / 2 / 32;
+#pragma unroll 1
+          for (int g = 0; g < GROUPS; ++g) {
+            const int col0 = hh * (D / 2) + g * 32;
+            uint32_t gv[32];
+            sm100::tmem_ld_32x32b_x32(trow + col0, gv);
+            sm100::tmem_ld_wait();
+            if (valid) {
+              const float* bias_g = p.bias + 4 * D + col0;
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gate_out) + srow * D + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float s[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[e] = sigmoid_tanh(__uint_as_float(gv[q * 8 + e]) + __ldg(bias_g + q * 8 + e));
+                uint4 pk;
+                pk.x = sm100::pack_bf16x2(s[0], s[1]);
+                pk.y = sm100::pack_bf16x2(s[2], s[3]);
+                pk.z = sm100::pack_bf16x2(s[4], s[5]);
+                pk.w = sm100::pack_bf16x2(s[6], s[7]);
+                dst[q] = pk;
+              }
+            }
+          }
+        }
+        sm100::tcgen05_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();  // single-lane roles reconverge with their warp
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    for (int s = 0; s < C::kWStages; ++s) {
+      const uint32_t ph = ctl->armed[s];
+      if (ph != 2) {
+        const uint64_t t0 = sm100::globaltimer_ns();
+        while (!sm100::mbar_test(&ctl->w_full[s], ph) && sm100::globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 2) {
+    sm100::tcgen05_fence_after_sync();
+    sm100::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+int gated_proj_smem_bytes(int D) {
+  if (D == 128) return smem_bytes<128>();
+  if (D == 256) return smem_bytes<256>();
+  return -1;
+}
+
+template <int D>
+static cudaError_t launch_t(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream) {
+  cudaError_t e =
+      cudaFuncSetAttribute(gated_proj_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
+  if (e != cudaSuccess) return e;
+  const int tiles_per_line = (args.n_walk + BM - 1) / BM;
+  const long total = static_cast<long>(args.batch) * args.n_lines * tiles_per_line;
+  if (total <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  gated_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream) {
+  if (args.D == 128) return launch_t<128>(tmW, args, num_sms, stream);
+  if (args.D == 256) return launch_t<256>(tmW, args, num_sms, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace trimul

@@ -1,0 +1,254 @@
+// Triangle contraction: for every channel plane l (l = d_loc * B + b)
+//     T_l[i, j] = sum_k  A_l[i, k] * B_l[j, k]          (bf16 in, fp32 accumulate, bf16 out)
+// A_l and B_l are row-major (rows x n_k) planes of the gated projections "a" and "b".  The
+// outgoing update feeds a[i,k], b[j,k]; the incoming update feeds the transposed planes
+// a^T[i,k] = a[k,i], b^T[j,k] = b[k,j], which the projection kernel writes directly, so this
+// kernel only ever sees K-major operands.
+// (Reference: the token-pair GEMM of fold_cp_ops/workflows/trimul_autotune.py:805-853 and the
+//  back store of fold_cp_ops/distributed/gemm_sm90_a2a.py; reshard layout reshard.py:277-289.)
+//
+// One persistent CTA per SM, 128 x 256 output tile, 64-wide K chunks through a TMA->smem ring,
+// tcgen05.mma (cta_group::1) into two 256-column TMEM accumulators so the epilogue of tile t
+// overlaps the main loop of tile t+1.  The epilogue converts to bf16 and stores 16-byte
+// vectors straight to the rank that owns the (i, j) token block: the back all-to-all rides the
+// store.  At cp=1 the only owner is this GPU.
+#include "trimul_common.cuh"
+#include "trimul_kernels.h"
+
+namespace trimul {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;  // 16 KB
+constexpr int kBBytes = BN * BK * 2;  // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+
+struct SmemCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  volatile uint32_t armed[kStages];  // parity of the phase the producer last armed, 2 = none
+};
+
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const TriContractArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  // SW128 tiles need 1024-byte alignment
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(tiles + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_i = (p.n_i + BM - 1) / BM;
+  const int tiles_j = (p.n_j + BN - 1) / BN;
+  const int tiles_per_plane = tiles_i * tiles_j;
+  const long total_tiles = static_cast<long>(tiles_per_plane) * p.planes;
+  const int num_k = (p.n_k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      sm100::mbar_init(&ctl->full[s], 1);
+      sm100::mbar_init(&ctl->empty[s], 1);
+      ctl->armed[s] = 2;
+    }
+    for (int a = 0; a < 2; ++a) {
+      sm100::mbar_init(&ctl->tmem_full[a], 1);
+      sm100::mbar_init(&ctl->tmem_empty[a], 4);  // one arrive per epilogue warp
+    }
+    ctl->abort_flag = 0;
+    sm100::mbar_init_fence();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tcgen05_fence_before_sync();
+  __syncthreads();
+  sm100::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const uint64_t tmo = p.timeout_ns;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      sm100::tma_prefetch_desc(&tmA);
+      sm100::tma_prefetch_desc(&tmB);
+      PipeState ps{0, 0};
+      for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const int plane = static_cast<int>(t / tiles_per_plane);
+        const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
+        const int ti = r / tiles_j;
+        const int tj = r - ti * tiles_j;
+        bool ok = true;
+        for (int kc = 0; kc < num_k; ++kc) {
+          if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelTriContract, 0, kc);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + ps.stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          ctl->armed[ps.stage] = ps.phase;
+          sm100::mbar_arrive_expect_tx(&ctl->full[ps.stage], kStageBytes);
+          sm100::tma_load_3d(sa, &tmA, &ctl->full[ps.stage], kc * BK, ti * BM, plane);
+          sm100::tma_load_3d(sb, &tmB, &ctl->full[ps.stage], kc * BK, tj * BN, plane);
+          ps.advance(kStages);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, BN);
+      PipeState ps{0, 0};
+      uint32_t acc = 0, acc_phase = 0;
+      for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        bool ok = sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo);
+        if (!ok) {
+          report_timeout(p.status, kKernelTriContract, 1, -1);
+          break;
+        }
+        sm100::tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kc = 0; kc < num_k; ++kc) {
+          if (!sm100::mbar_wait(&ctl->full[ps.stage], ps.phase, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelTriContract, 1, kc);
+            ok = false;
+            break;
+          }
+          sm100::tcgen05_fence_after_sync();
+          const uint32_t sa = sm100::smem_u32(tiles + ps.stage * kStageBytes);
+          const uint64_t da = sm100::umma_desc_kmajor_sw128(sa);
+          const uint64_t db = sm100::umma_desc_kmajor_sw128(sa + kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            // +32 bytes per 16-element K step inside the 128-byte swizzle row (>>4 => +2)
+            sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0);
+          }
+          sm100::umma_commit(&ctl->empty[ps.stage]);  // frees the smem stage when the MMAs retire
+          ps.advance(kStages);
+        }
+        if (!ok) break;
+        sm100::umma_commit(&ctl->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc = 0, acc_phase = 0;
+    const long owner_plane_elems = static_cast<long>(p.ni_loc) * p.nj_loc;
+    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int plane = static_cast<int>(t / tiles_per_plane);
+      const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
+      const int ti = r / tiles_j;
+      const int tj = r - ti * tiles_j;
+      bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
+      ok = __all_sync(0xffffffffu, ok);  // the warp leaves together: tcgen05.ld is warp-collective
+      if (!ok) {
+        report_timeout(p.status, kKernelTriContract, 2, static_cast<int>(t));
+        break;
+      }
+      sm100::tcgen05_fence_after_sync();
+      const int i = ti * BM + quarter * 32 + lane;
+      const bool row_ok = i < p.n_i;
+      const int i_blk = row_ok ? i / p.ni_loc : 0;
+      const int i_l = i - i_blk * p.ni_loc;
+      // destination plane index on the owner: (chan_offset + d_loc) * B + b  == chan_offset*B + plane
+      const long dst_plane = static_cast<long>(p.chan_offset) * p.batch + plane;
+      const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        sm100::tmem_ld_32x32b_x32(taddr_row + c * 32, v);
+        sm100::tmem_ld_wait();
+        const int j0 = tj * BN + c * 32;
+        if (row_ok && j0 < p.n_j) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int j = j0 + q * 8;
+            if (j < p.n_j) {  // n_j % 8 == 0: a 16-byte vector never straddles the edge or an owner
+              const int j_blk = j / p.nj_loc;
+              const int j_l = j - j_blk * p.nj_loc;
+              __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.out.ptr[i_blk * p.cp1 + j_blk]);
+              uint4 pk;
+              pk.x = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(base + dst_plane * owner_plane_elems + static_cast<long>(i_l) * p.nj_loc +
+                                        j_l) = pk;
+            }
+          }
+        }
+      }
+      sm100::tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();  // single-lane roles reconverge with their warp
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // a wait expired somewhere: let TMA copies still in flight land before the CTA exits
+    for (int s = 0; s < kStages; ++s) {
+      const uint32_t ph = ctl->armed[s];
+      if (ph != 2) {
+        const uint64_t t0 = sm100::globaltimer_ns();
+        while (!sm100::mbar_test(&ctl->full[s], ph) && sm100::globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tcgen05_fence_after_sync();
+    sm100::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+int tri_contract_smem_bytes() { return kSmemBytes; }
+
+cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, const TriContractArgs& args,
+                                int num_sms, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(tri_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int tiles_i = (args.n_i + BM - 1) / BM;
+  const int tiles_j = (args.n_j + BN - 1) / BN;
+  const long total = static_cast<long>(tiles_i) * tiles_j * args.planes;
+  if (total <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  tri_contract_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, args);
+  return cudaGetLastError();
+}
+
+}  // namespace trimul

@@ -1,0 +1,364 @@
+// C ABI of libtrimul_sm100.so (declared in include/trimul_sm100.h): argument checking, geometry
+// derivation, TMA descriptor encoding, and the launches.  No allocation, no hidden streams.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/trimul_sm100.h"
+#include "trimul_kernels.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* where) {
+  return fail(TRIMUL_ERR_CUDA, "%s: %s", where, cudaGetErrorString(e));
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: no link-time libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// bf16 tensor, innermost dim contiguous, 128-byte swizzle, zero fill out of bounds.
+int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+              const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(TRIMUL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bx[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim,
+                  gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TRIMUL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TRIMUL_OK;
+}
+
+int num_sms_current() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+struct Derived {
+  int cp, r0, r1, ni_loc, nj_loc, d_loc, d_loc_log2;
+  long i_off, j_off, rows;
+};
+
+int check_geom(const trimul_geom_t* g, Derived* d) {
+  if (g == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "geom is NULL");
+  if (g->batch < 1 || g->n < 1) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "batch and n must be >= 1");
+  if (g->d != 128 && g->d != 256)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported (128 or 256)", g->d);
+  if (g->cp0 < 1 || g->cp1 < 1 || g->cp0 * g->cp1 > TRIMUL_MAX_PEERS)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "cp grid %d x %d must have 1..%d ranks", g->cp0, g->cp1,
+                TRIMUL_MAX_PEERS);
+  const int cp = g->cp0 * g->cp1;
+  if (g->rank < 0 || g->rank >= cp) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "rank %d outside cp=%d", g->rank, cp);
+  if (g->direction != TRIMUL_OUTGOING && g->direction != TRIMUL_INCOMING)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "direction must be 0 (outgoing) or 1 (incoming)");
+  if (g->n % 8 != 0) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d must be a multiple of 8", g->n);
+  if (g->n % g->cp0 != 0 || g->n % g->cp1 != 0)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d must divide by each cp axis (%d, %d)", g->n, g->cp0, g->cp1);
+  if (g->d % cp != 0) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "d=%d must divide by cp=%d", g->d, cp);
+  d->cp = cp;
+  d->r0 = g->rank / g->cp1;
+  d->r1 = g->rank % g->cp1;
+  d->ni_loc = g->n / g->cp0;
+  d->nj_loc = g->n / g->cp1;
+  if (cp > 1 && (d->ni_loc % 8 != 0 || d->nj_loc % 8 != 0))
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token extents (%d, %d) must be multiples of 8", d->ni_loc,
+                d->nj_loc);
+  d->d_loc = g->d / cp;
+  int lg = 0;
+  while ((1 << lg) < d->d_loc) ++lg;
+  if ((1 << lg) != d->d_loc)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "d/cp=%d must be a power of two", d->d_loc);
+  d->d_loc_log2 = lg;
+  d->i_off = static_cast<long>(d->r0) * d->ni_loc;
+  d->j_off = static_cast<long>(d->r1) * d->nj_loc;
+  d->rows = static_cast<long>(g->batch) * d->ni_loc * d->nj_loc;
+  return TRIMUL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// weight packing kernel (runs once per layer)
+// ---------------------------------------------------------------------------------------------
+__global__ void pack_weights_kernel(int d, const __nv_bfloat16* p_in, const __nv_bfloat16* g_in,
+                                    const __nv_bfloat16* g_out, const float* p_in_b, const float* g_in_b,
+                                    const float* g_out_b, __nv_bfloat16* w_packed, float* bias_packed) {
+  const int row = blockIdx.x;  // packed row 0 .. 5d-1
+  const int ch = d / 2;
+  const int chunk = row / d;
+  const int rr = row - chunk * d;
+  const __nv_bfloat16* src;
+  float bias;
+  if (chunk < 4) {
+    const bool is_gate = rr >= ch;
+    const int src_row = chunk * ch + (is_gate ? rr - ch : rr);  // row of the (2d, d) matrix
+    src = (is_gate ? g_in : p_in) + static_cast<long>(src_row) * d;
+    const float* b = is_gate ? g_in_b : p_in_b;
+    bias = b ? b[src_row] : 0.0f;
+  } else {
+    src = g_out + static_cast<long>(rr) * d;
+    bias = g_out_b ? g_out_b[rr] : 0.0f;
+  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x) w_packed[static_cast<long>(row) * d + c] = src[c];
+  if (threadIdx.x == 0) bias_packed[row] = bias;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* trimul_sm100_last_error(void) { return g_err; }
+
+int trimul_sm100_query(int device, trimul_caps_t* out) {
+  if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "caps is NULL");
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+  out->cc_major = prop.major;
+  out->cc_minor = prop.minor;
+  out->num_sms = prop.multiProcessorCount;
+  out->max_smem_per_block = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+  out->supported = (prop.major == 10) ? 1 : 0;
+  if (!out->supported)
+    return fail(TRIMUL_ERR_UNSUPPORTED_ARCH,
+                "fold-cp-ops (B200 build) requires SM100 (B200); got sm_%d%d. No other architecture has a code path.",
+                prop.major, prop.minor);
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "workspace is NULL");
+  const uint64_t nn = static_cast<uint64_t>(geom->n) * geom->n;
+  out->ab_bytes = 2ull * d.d_loc * geom->batch * nn * 2ull;
+  out->tri_bytes = static_cast<uint64_t>(geom->d) * d.rows * 2ull;
+  out->gate_bytes = static_cast<uint64_t>(d.rows) * geom->d * 2ull;
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
+                              const float* p_in_b, const float* g_in_b, const float* g_out_b, void* w_packed,
+                              float* bias_packed, trimul_stream_t stream) {
+  if (d != 128 && d != 256) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
+  if (!p_in_w || !g_in_w || !g_out_w || !w_packed || !bias_packed)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "pack_weights: NULL weight pointer");
+  pack_weights_kernel<<<5 * d, 128, 0, stream>>>(
+      d, static_cast<const __nv_bfloat16*>(p_in_w), static_cast<const __nv_bfloat16*>(g_in_w),
+      static_cast<const __nv_bfloat16*>(g_out_w), p_in_b, g_in_b, g_out_b, static_cast<__nv_bfloat16*>(w_packed),
+      bias_packed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pack_weights launch");
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
+                               const float* ln_w, const float* ln_b, const void* w_packed,
+                               const float* bias_packed, void* const* ab_peers, void* gate_out,
+                               trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (!x || !ln_w || !w_packed || !bias_packed || !ab_peers || !gate_out)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: NULL pointer");
+  if (mask_kind < 0 || mask_kind > 3 || (mask_kind != 0 && mask == nullptr))
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: bad mask_kind %d", mask_kind);
+  const int D = geom->d;
+  CUtensorMap tmW;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(5 * D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    rc = make_tmap(&tmW, w_packed, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  trimul::GatedProjArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x = x;
+  a.mask = mask_kind ? mask : nullptr;
+  a.mask_kind = mask_kind;
+  a.ln_w = ln_w;
+  a.ln_b = ln_b;
+  a.bias = bias_packed;
+  a.eps = geom->eps;
+  a.D = D;
+  a.batch = geom->batch;
+  a.batch_rows = static_cast<long>(d.ni_loc) * d.nj_loc;
+  const long n = geom->n;
+  if (geom->direction == TRIMUL_OUTGOING) {
+    if (geom->cp1 == 1) {
+      // rows (b, i, :) are contiguous in x and in the destination plane: walk the whole block
+      a.n_lines = 1;
+      a.n_walk = static_cast<int>(static_cast<long>(d.ni_loc) * d.nj_loc);
+      a.line_rows = 0;
+      a.walk_rows = 1;
+      a.dst_base = d.i_off * n;
+      a.dst_line = 0;
+      if (static_cast<long>(d.ni_loc) * d.nj_loc > 0x7fffffffL)
+        return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token block too large");
+    } else {
+      a.n_lines = d.ni_loc;
+      a.n_walk = d.nj_loc;
+      a.line_rows = d.nj_loc;
+      a.walk_rows = 1;
+      a.dst_base = d.i_off * n + d.j_off;
+      a.dst_line = n;
+    }
+  } else {
+    a.n_lines = d.nj_loc;
+    a.n_walk = d.ni_loc;
+    a.line_rows = 1;
+    a.walk_rows = d.nj_loc;
+    a.dst_base = d.j_off * n + d.i_off;
+    a.dst_line = n;
+  }
+  for (int s = 0; s < d.cp; ++s) {
+    if (ab_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ab_peers[%d] is NULL", s);
+    a.ab.ptr[s] = ab_peers[s];
+  }
+  a.d_loc_log2 = d.d_loc_log2;
+  a.plane_elems = n * n;
+  a.gate_out = gate_out;
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  cudaError_t e = trimul::launch_gated_proj(tmW, a, num_sms_current(), stream);
+  if (e != cudaSuccess) return cuda_fail(e, "ln_gated_proj launch");
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, void* const* tri_peers,
+                              trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (!ab_local || !tri_peers) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_contract: NULL pointer");
+  const uint64_t n = static_cast<uint64_t>(geom->n);
+  const uint64_t planes = static_cast<uint64_t>(d.d_loc) * geom->batch;
+  CUtensorMap tmA, tmB;
+  {
+    const uint64_t dims[3] = {n, n, planes};
+    const uint64_t strides[2] = {n * 2, n * n * 2};
+    const uint32_t boxA[3] = {64, 128, 1};
+    const uint32_t boxB[3] = {64, 256, 1};
+    rc = make_tmap(&tmA, ab_local, 3, dims, strides, boxA);
+    if (rc != TRIMUL_OK) return rc;
+    const uint8_t* b_base = static_cast<const uint8_t*>(ab_local) + planes * n * n * 2;
+    rc = make_tmap(&tmB, b_base, 3, dims, strides, boxB);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  trimul::TriContractArgs a;
+  memset(&a, 0, sizeof(a));
+  a.planes = static_cast<int>(planes);
+  a.batch = geom->batch;
+  a.n_i = a.n_j = a.n_k = geom->n;
+  for (int s = 0; s < d.cp; ++s) {
+    if (tri_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_peers[%d] is NULL", s);
+    a.out.ptr[s] = tri_peers[s];
+  }
+  a.ni_loc = d.ni_loc;
+  a.nj_loc = d.nj_loc;
+  a.cp1 = geom->cp1;
+  a.chan_offset = geom->rank * d.d_loc;
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  cudaError_t e = trimul::launch_tri_contract(tmA, tmB, a, num_sms_current(), stream);
+  if (e != cudaSuccess) return cuda_fail(e, "tri_contract launch");
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate,
+                             const float* ln_w, const float* ln_b, const void* w_out, const float* bias_out,
+                             void* out, trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (!tri_local || !gate || !ln_w || !w_out || !out)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_out_proj: NULL pointer");
+  const int D = geom->d;
+  CUtensorMap tmW;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    rc = make_tmap(&tmW, w_out, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  trimul::OutProjArgs a;
+  memset(&a, 0, sizeof(a));
+  a.tri = tri_local;
+  a.gate = gate;
+  a.ln_w = ln_w;
+  a.ln_b = ln_b;
+  a.bias = bias_out;
+  a.out = out;
+  a.eps = geom->eps;
+  a.D = D;
+  a.rows = d.rows;
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  cudaError_t e = trimul::launch_out_proj(tmW, a, num_sms_current(), stream);
+  if (e != cudaSuccess) return cuda_fail(e, "ln_out_proj launch");
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
+                         const float* ln_in_w, const float* ln_in_b, const void* w_packed,
+                         const float* bias_packed, const float* ln_out_w, const float* ln_out_b,
+                         const void* w_out, const float* bias_out, void* ab, void* tri, void* gate, void* out,
+                         trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+  if (geom == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "geom is NULL");
+  if (geom->cp0 != 1 || geom->cp1 != 1)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "trimul_sm100_forward is the single-GPU chain; cp grid must be 1 x 1");
+  void* ab_peers[1] = {ab};
+  void* tri_peers[1] = {tri};
+  int rc = trimul_sm100_ln_gated_proj(geom, x, mask, mask_kind, ln_in_w, ln_in_b, w_packed, bias_packed, ab_peers,
+                                      gate, status, timeout_ns, stream);
+  if (rc != TRIMUL_OK) return rc;
+  rc = trimul_sm100_tri_contract(geom, ab, tri_peers, status, timeout_ns, stream);
+  if (rc != TRIMUL_OK) return rc;
+  return trimul_sm100_ln_out_proj(geom, tri, gate, ln_out_w, ln_out_b, w_out, bias_out, out, status, timeout_ns,
+                                  stream);
+}
+
+}  // extern "C"

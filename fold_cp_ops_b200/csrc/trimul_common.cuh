@@ -1,0 +1,56 @@
+// Shared definitions for the three TriMul kernels: status word, peer table, launch helpers.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace trimul {
+
+constexpr int kMaxPeers = 8;  // one NVSwitch domain: up to 8 ranks in the cp group
+
+// Kernel ids reported in the status word.
+enum KernelId : int { kKernelGatedProj = 1, kKernelTriContract = 2, kKernelOutProj = 3, kKernelPeerSync = 4 };
+
+// status[0] = 0 OK | 1 bounded wait expired ; [1] kernel id ; [2] block ; [3] role ; [4] detail
+struct DeviceStatus {
+  int code;
+  int kernel;
+  int block;
+  int role;
+  int detail;
+  int pad[3];
+};
+
+__device__ __forceinline__ void report_timeout(DeviceStatus* st, int kernel, int role, int detail) {
+  if (st == nullptr) return;
+  if (atomicCAS(&st->code, 0, 1) == 0) {
+    st->kernel = kernel;
+    st->block = static_cast<int>(blockIdx.x);
+    st->role = role;
+    st->detail = detail;
+    __threadfence_system();
+  }
+}
+
+// Base pointers of one logical buffer on every rank of the cp group (index = flat cp rank).
+// At cp=1 only ptr[0] is used and it is local memory.
+struct PeerPtrs {
+  void* ptr[kMaxPeers];
+};
+
+// Ring-buffer stage/phase bookkeeping for mbarrier pipelines.
+struct PipeState {
+  uint32_t stage;
+  uint32_t phase;
+  __device__ __forceinline__ void advance(uint32_t nstages) {
+    if (++stage == nstages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+};
+
+}  // namespace trimul

@@ -1,0 +1,89 @@
+// Internal C++ interface between the C-ABI layer and the three kernels.  Plain structs only.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "trimul_common.cuh"
+
+namespace trimul {
+
+// ---------------------------------------------------------------------------------------------
+// K_A  LayerNorm + gated dual projection (+ output gate), front reshard fused in the store
+// ---------------------------------------------------------------------------------------------
+// Token walk: the local pair block is x[b, i, j, :] with row index (b*Ni + i)*Nj + j.  A tile is
+// up to 128 tokens along the "walk" coordinate of one "line":
+//     row(b, line, w) = b * batch_rows + line * line_rows + w * walk_rows
+// outgoing: line = i, walk = j  (line_rows = Nj, walk_rows = 1)
+// incoming: line = j, walk = i  (line_rows = 1,  walk_rows = Nj)
+// so that the 128 tokens of a tile are consecutive along the CONTRACTION index k of the plane
+// they land in, and the store to the channel-major operand plane is contiguous.
+struct GatedProjArgs {
+  const void* x;         // bf16 (rows, D)
+  const void* mask;      // nullable; one scalar per row
+  int mask_kind;         // 0 none, 1 bf16, 2 fp32, 3 uint8/bool
+  const float* ln_w;     // (D,)
+  const float* ln_b;     // (D,) or nullptr
+  const float* bias;     // (5*D,) fp32 in PACKED row order (zeros where the layer has no bias)
+  float eps;
+  int D;
+  int batch;
+  int n_lines;           // lines per batch plane
+  int n_walk;            // tokens per line
+  long batch_rows, line_rows, walk_rows;
+  // destination of the a / b planes: ptr[s] = base of rank s's operand buffer laid out
+  // (2, D_loc, B, plane_rows, plane_cols); this rank fills [dst_base + line*dst_line + w]
+  PeerPtrs ab;
+  int d_loc_log2;        // log2(D / cp)
+  long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
+  long dst_base;         // element offset of (line 0, w 0) inside a plane
+  long dst_line;         // element stride between lines inside a plane
+  void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
+  DeviceStatus* status;
+  uint64_t timeout_ns;
+};
+
+int gated_proj_smem_bytes(int D);
+cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// K_B  per-channel N x N x N contraction, back reshard fused in the store
+// ---------------------------------------------------------------------------------------------
+struct TriContractArgs {
+  int planes;       // D_loc * B, plane l = d_loc * B + b
+  int batch;        // B
+  int n_i, n_j, n_k;
+  // destination: rank (i / ni_loc) * cp1 + (j / nj_loc) owns token block; its buffer is laid out
+  // (D, B, ni_loc, nj_loc) and this rank fills channels [chan_offset, chan_offset + D_loc)
+  PeerPtrs out;
+  int ni_loc, nj_loc, cp1;
+  int chan_offset;
+  DeviceStatus* status;
+  uint64_t timeout_ns;
+};
+
+int tri_contract_smem_bytes();
+cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, const TriContractArgs& args,
+                                int num_sms, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// K_C  output LayerNorm + output projection, gated
+// ---------------------------------------------------------------------------------------------
+struct OutProjArgs {
+  const void* tri;       // bf16 (D, rows): channel-major planes, plane stride = rows
+  const void* gate;      // bf16 (rows, D)
+  const float* ln_w;     // (D,)
+  const float* ln_b;     // (D,) or nullptr
+  const float* bias;     // (D,) or nullptr
+  void* out;             // bf16 (rows, D)
+  float eps;
+  int D;
+  long rows;
+  DeviceStatus* status;
+  uint64_t timeout_ns;
+};
+
+int out_proj_smem_bytes(int D);
+cudaError_t launch_out_proj(const CUtensorMap& tmW, const OutProjArgs& args, int num_sms, cudaStream_t stream);
+
+}  // namespace trimul

@@ -1,0 +1,168 @@
+"""Per-kernel Python entry points over the C ABI, taking torch CUDA tensors.
+
+Each function checks dtypes / contiguity, passes raw device pointers and the current CUDA stream
+to ``libtrimul_sm100.so`` and returns nothing: outputs are written into caller-provided tensors.
+They are the unit the parity tests and the profiler drive; the engine chains them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+DEFAULT_TIMEOUT_NS = 2_000_000_000
+
+_MASK_KINDS = {torch.bfloat16: _lib.MASK_BF16, torch.float32: _lib.MASK_FP32,
+               torch.uint8: _lib.MASK_U8, torch.bool: _lib.MASK_U8}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor; the TriMul kernels have no CPU path")
+    if t.dtype is not dtype:
+        raise ValueError(f"{name} must be {dtype}; got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def make_geom(batch: int, n: int, d: int, direction: str, eps: float, cp0: int = 1, cp1: int = 1,
+              rank: int = 0) -> _lib.Geom:
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"direction must be 'outgoing' or 'incoming'; got {direction!r}")
+    return _lib.Geom(int(batch), int(n), int(d), int(cp0), int(cp1), int(rank),
+                     _lib.OUTGOING if direction == "outgoing" else _lib.INCOMING, float(eps))
+
+
+def device_caps(device: int) -> _lib.Caps:
+    """Query the device and raise unless it is compute capability 10.x."""
+    caps = _lib.Caps()
+    rc = _lib.load().trimul_sm100_query(int(device), C.byref(caps))
+    if rc == _lib.ERR_UNSUPPORTED_ARCH:
+        raise RuntimeError(_lib.last_error())
+    _lib.check(rc, "trimul_sm100_query")
+    return caps
+
+
+def workspace_bytes(geom: _lib.Geom) -> _lib.Workspace:
+    ws = _lib.Workspace()
+    _lib.check(_lib.load().trimul_sm100_workspace(C.byref(geom), C.byref(ws)), "trimul_sm100_workspace")
+    return ws
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device status record (8 x int32) for the bounded waits to report into."""
+    return torch.zeros(8, dtype=torch.int32, device=device)
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait expired; the kernel returned early and the context is intact."""
+
+
+_KERNEL_NAMES = {1: "ln_gated_proj", 2: "tri_contract", 3: "ln_out_proj", 4: "peer_sync"}
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Synchronising read of the status record; raises :class:`DeviceWaitTimeout` if a wait expired."""
+    s = status.tolist()
+    if s[0] != 0:
+        status.zero_()
+        raise DeviceWaitTimeout(
+            f"bounded wait expired in kernel {_KERNEL_NAMES.get(s[1], s[1])}: block {s[2]}, role {s[3]}, "
+            f"detail {s[4]}; outputs of this forward are invalid"
+        )
+
+
+def pack_weights(d: int, p_in_w, g_in_w, g_out_w, p_in_b=None, g_in_b=None, g_out_b=None):
+    """Regroup the input-side weights into the chunk order the projection kernel streams.
+
+    Returns ``(w_packed (5d, d) bf16, bias_packed (5d,) fp32)``.
+    """
+    for t, nm, shp in ((p_in_w, "p_in_w", (2 * d, d)), (g_in_w, "g_in_w", (2 * d, d)), (g_out_w, "g_out_w", (d, d))):
+        _require(t, torch.bfloat16, nm)
+        if tuple(t.shape) != shp:
+            raise ValueError(f"{nm} must have shape {shp}; got {tuple(t.shape)}")
+    for t, nm in ((p_in_b, "p_in_b"), (g_in_b, "g_in_b"), (g_out_b, "g_out_b")):
+        if t is not None:
+            _require(t, torch.float32, nm)
+    dev = p_in_w.device
+    w_packed = torch.empty(5 * d, d, dtype=torch.bfloat16, device=dev)
+    bias_packed = torch.empty(5 * d, dtype=torch.float32, device=dev)
+    rc = _lib.load().trimul_sm100_pack_weights(d, _ptr(p_in_w), _ptr(g_in_w), _ptr(g_out_w), _ptr(p_in_b),
+                                               _ptr(g_in_b), _ptr(g_out_b), _ptr(w_packed), _ptr(bias_packed),
+                                               _stream())
+    _lib.check(rc, "trimul_sm100_pack_weights")
+    return w_packed, bias_packed
+
+
+def _mask_args(mask: Optional[torch.Tensor]):
+    if mask is None:
+        return None, _lib.MASK_NONE
+    if not mask.is_cuda or not mask.is_contiguous():
+        raise ValueError("mask must be a contiguous CUDA tensor")
+    kind = _MASK_KINDS.get(mask.dtype)
+    if kind is None:
+        raise ValueError(f"mask dtype {mask.dtype} is not supported (bf16, fp32, uint8, bool)")
+    return mask.data_ptr(), kind
+
+
+def _ptr_array(ptrs: Sequence[int]):
+    arr = (C.c_void_p * len(ptrs))(*[C.c_void_p(int(p)) for p in ptrs])
+    return arr
+
+
+def ln_gated_proj(geom, x, mask, ln_w, ln_b, w_packed, bias_packed, ab_peer_ptrs: Sequence[int], gate_out,
+                  status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    _require(x, torch.bfloat16, "x")
+    _require(ln_w, torch.float32, "ln_w")
+    if ln_b is not None:
+        _require(ln_b, torch.float32, "ln_b")
+    _require(gate_out, torch.bfloat16, "gate_out")
+    mptr, mkind = _mask_args(mask)
+    rc = _lib.load().trimul_sm100_ln_gated_proj(C.byref(geom), _ptr(x), mptr, mkind, _ptr(ln_w), _ptr(ln_b),
+                                                _ptr(w_packed), _ptr(bias_packed), _ptr_array(ab_peer_ptrs),
+                                                _ptr(gate_out), _ptr(status), int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_ln_gated_proj")
+
+
+def tri_contract(geom, ab_local, tri_peer_ptrs: Sequence[int], status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    _require(ab_local, torch.bfloat16, "ab_local")
+    rc = _lib.load().trimul_sm100_tri_contract(C.byref(geom), _ptr(ab_local), _ptr_array(tri_peer_ptrs),
+                                               _ptr(status), int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_tri_contract")
+
+
+def ln_out_proj(geom, tri_local, gate, ln_w, ln_b, w_out, bias_out, out, status,
+                timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    _require(tri_local, torch.bfloat16, "tri_local")
+    _require(gate, torch.bfloat16, "gate")
+    _require(ln_w, torch.float32, "ln_w")
+    _require(w_out, torch.bfloat16, "w_out")
+    _require(out, torch.bfloat16, "out")
+    rc = _lib.load().trimul_sm100_ln_out_proj(C.byref(geom), _ptr(tri_local), _ptr(gate), _ptr(ln_w), _ptr(ln_b),
+                                              _ptr(w_out), _ptr(bias_out), _ptr(out), _ptr(status),
+                                              int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_ln_out_proj")
+
+
+def forward_single(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, ln_out_w, ln_out_b, w_out, bias_out,
+                   ab, tri, gate, out, status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    """The whole cp=1 chain through ``trimul_sm100_forward``."""
+    _require(x, torch.bfloat16, "x")
+    _require(out, torch.bfloat16, "out")
+    mptr, mkind = _mask_args(mask)
+    rc = _lib.load().trimul_sm100_forward(C.byref(geom), _ptr(x), mptr, mkind, _ptr(ln_in_w), _ptr(ln_in_b),
+                                          _ptr(w_packed), _ptr(bias_packed), _ptr(ln_out_w), _ptr(ln_out_b),
+                                          _ptr(w_out), _ptr(bias_out), _ptr(ab), _ptr(tri), _ptr(gate), _ptr(out),
+                                          _ptr(status), int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_forward")

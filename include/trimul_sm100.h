@@ -1,0 +1,141 @@
+/*
+ * trimul_sm100.h -- C ABI of libtrimul_sm100.so: the Blackwell (sm_100a) kernels behind the
+ * context-parallel triangle multiplicative update ("TriMul") forward.
+ *
+ * The reference package (NVIDIA-BioNeMo/fold-cp-ops) has no native code: its kernels are CuTe-DSL
+ * Python objects JIT-compiled for SM90 and launched from Python.  Each entry point below names the
+ * reference Python interface whose job it takes over (path inside the reference project : line).
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative TRIMUL_ERR_* code; nothing throws or exits;
+ *   - every pointer is caller-owned DEVICE memory unless stated otherwise; nothing is allocated or
+ *     freed here and there are no hidden streams: work is enqueued on the stream that is passed;
+ *   - all activations and weights are bf16, LayerNorm gains/biases and projection biases are fp32;
+ *   - device-side waits are bounded: on expiry a kernel writes a trimul_status_t record and returns
+ *     normally, so the CUDA context stays usable.  The caller owns the status record (8 x int32,
+ *     zero it once) and reads it after synchronising the stream.
+ */
+#ifndef TRIMUL_SM100_H_
+#define TRIMUL_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRIMUL_OK 0
+#define TRIMUL_ERR_INVALID_ARGUMENT (-1)
+#define TRIMUL_ERR_UNSUPPORTED_ARCH (-2)
+#define TRIMUL_ERR_CUDA (-3)
+#define TRIMUL_ERR_UNSUPPORTED_SHAPE (-4)
+
+#define TRIMUL_MAX_PEERS 8
+
+#define TRIMUL_MASK_NONE 0
+#define TRIMUL_MASK_BF16 1
+#define TRIMUL_MASK_FP32 2
+#define TRIMUL_MASK_U8 3
+
+#define TRIMUL_OUTGOING 0
+#define TRIMUL_INCOMING 1
+
+typedef struct CUstream_st* trimul_stream_t;
+
+/* Device capabilities.  Mirrors the architecture gate of fold_cp_ops/_internal/arch.py:145-170
+ * (`check_arch_supported`), inverted: this library needs compute capability 10.x. */
+typedef struct trimul_caps {
+  int32_t cc_major;
+  int32_t cc_minor;
+  int32_t num_sms;
+  int32_t max_smem_per_block;
+  int32_t supported; /* 1 when the kernels can run on this device */
+} trimul_caps_t;
+
+/* Geometry of one forward on one rank.  The global pair tensor is (batch, n, n, d); the token grid
+ * is split cp0 x cp1 (rows x columns) and this rank is flat cp rank `rank` = r0 * cp1 + r1, the
+ * row-major peer order of fold_cp_ops/distributed/pe_map.py:265-283.  cp0 = cp1 = 1 is the
+ * single-GPU case. */
+typedef struct trimul_geom {
+  int32_t batch;
+  int32_t n;
+  int32_t d;
+  int32_t cp0;
+  int32_t cp1;
+  int32_t rank;
+  int32_t direction; /* TRIMUL_OUTGOING | TRIMUL_INCOMING */
+  float eps;
+} trimul_geom_t;
+
+/* Record a kernel leaves behind when a bounded wait expires. */
+typedef struct trimul_status {
+  int32_t code;   /* 0 = OK, 1 = a bounded wait expired */
+  int32_t kernel; /* 1 gated projection, 2 contraction, 3 output projection, 4 peer sync */
+  int32_t block;
+  int32_t role;
+  int32_t detail;
+  int32_t pad[3];
+} trimul_status_t;
+
+/* Bytes of each buffer a rank needs for `geom` (all bf16):
+ *   ab   : operand planes this rank contracts, (2, d/cp, batch, n, n)   -- written by every rank
+ *   tri  : contraction result for this rank's tokens, (d, batch, n/cp0, n/cp1) -- written by every rank
+ *   gate : output gate for this rank's tokens, (batch, n/cp0, n/cp1, d)  -- local only
+ * Replaces the receive-buffer sizing of `ReshardLayout` (fold_cp_ops/distributed/reshard.py:63-289)
+ * and `_symmetric_empty` (fold_cp_ops/distributed/workflows/trimul_autotuned.py:150). */
+typedef struct trimul_workspace {
+  uint64_t ab_bytes;
+  uint64_t tri_bytes;
+  uint64_t gate_bytes;
+} trimul_workspace_t;
+
+int trimul_sm100_query(int device, trimul_caps_t* out);
+int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out);
+const char* trimul_sm100_last_error(void);
+
+/* Pack the input-side weights once at construction: rows of p_in / g_in / g_out (each row-major
+ * (out, in), bf16) are regrouped into five d-row chunks [a_lo|a_hi|b_lo|b_hi: d/2 projection rows
+ * then the d/2 matching gate rows][g_out: d rows]; biases (fp32, any may be NULL) are packed the
+ * same way.  w_packed: (5d, d) bf16; bias_packed: (5d) fp32.
+ * Replaces `interleave_dual_weights` (fold_cp_ops/kernels/dual_gated_gemm.py:958). */
+int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
+                              const float* p_in_b, const float* g_in_b, const float* g_out_b, void* w_packed,
+                              float* bias_packed, trimul_stream_t stream);
+
+/* Stage 1+2: input LayerNorm fused into the gated dual projection, front reshard fused in the
+ * store.  x: this rank's (batch, n/cp0, n/cp1, d) block; mask: one scalar per local token or NULL;
+ * ab_peers[s]: base of rank s's `ab` buffer (cp0*cp1 entries; entry `rank` is local memory);
+ * gate_out: local `gate` buffer.
+ * Replaces `layernorm_fwd` (fold_cp_ops/kernels/layernorm.py:730) + `DualGatedGemmDistStore.run`
+ * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:1744) + the g_out half of
+ * `layernorm_dual_gated_gemm` (fold_cp_ops/kernels/layernorm_dual_gated_gemm.py:5342). */
+int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
+                               const float* ln_w, const float* ln_b, const void* w_packed,
+                               const float* bias_packed, void* const* ab_peers, void* gate_out,
+                               trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+
+/* Stage 3: per-channel n x n x n contraction of this rank's `ab` planes, back reshard fused in the
+ * store.  tri_peers[s]: base of rank s's `tri` buffer.
+ * Replaces `GemmA2AStore.run` (fold_cp_ops/distributed/workflows/trimul_autotuned.py:2548) and the
+ * cp=1 `_gemm1` (fold_cp_ops/workflows/trimul_autotune.py:805). */
+int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, void* const* tri_peers,
+                              trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+
+/* Stage 4: output LayerNorm fused with the output projection, gated.  out: (batch, n/cp0, n/cp1, d).
+ * Replaces `_consume` (fold_cp_ops/distributed/workflows/trimul_autotuned.py:3482-3550). */
+int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate,
+                             const float* ln_w, const float* ln_b, const void* w_out, const float* bias_out,
+                             void* out, trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+
+/* The whole single-GPU forward (cp0 = cp1 = 1): stages 1-4 back to back on `stream`.
+ * Replaces `trimul_autotuned` (fold_cp_ops/workflows/trimul_autotune.py:1531). */
+int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
+                         const float* ln_in_w, const float* ln_in_b, const void* w_packed,
+                         const float* bias_packed, const float* ln_out_w, const float* ln_out_b,
+                         const void* w_out, const float* bias_out, void* ab, void* tri, void* gate, void* out,
+                         trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIMUL_SM100_H_ */

@@ -1,0 +1,106 @@
+"""The CPU oracle is pinned against the reference: golden vectors made by the reference's own
+``trimul_ref`` (tests/golden/make_golden.py) and, when the reference checkout is importable, the
+reference called directly."""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.trimul_oracle import (bf16_round_case, cp1_bound, make_case, tolerance_bound, trimul_oracle,
+                                  trimul_stages, weights_of)
+from tests.golden.make_golden import CASES, input_digest
+
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+
+
+def _case(name):
+    kw = dict(CASES[name])
+    direction = kw.pop("direction")
+    return bf16_round_case(make_case(**kw)), direction
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_inputs_are_reproducible(name, golden):
+    case, _ = _case(name)
+    want = bytes(golden[name + "__digest"].tobytes()).hex()
+    assert input_digest(case) == want, "seeded inputs differ from the ones the golden vectors were made with"
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_oracle_matches_reference_golden(name, golden):
+    case, direction = _case(name)
+    got = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    ref = torch.from_numpy(golden[name])
+    assert got.shape == ref.shape and got.dtype == torch.float32
+    # both are fp32 evaluations of the same twelve ops; only summation order may differ
+    err = (got - ref).abs()
+    assert err.max().item() <= 2e-5 * max(1.0, ref.abs().max().item()), err.max().item()
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_oracle_matches_reference_eager_module_golden(direction, golden):
+    case = bf16_round_case(make_case(B=1, N=16, D=128, seed=107, ln_affine=True, bias="none", mask="random"))
+    got = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    ref = torch.from_numpy(golden[f"eager_{direction}_n16_d128"])
+    assert (got - ref).abs().max().item() <= 2e-5 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "fold_cp_ops")),
+                    reason="reference checkout not present")
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("bias,mask", [("none", "none"), ("all", "random"), ("out", "pad")])
+def test_oracle_matches_live_reference(direction, bias, mask):
+    sys.dont_write_bytecode = True
+    if REFERENCE_ROOT not in sys.path:
+        sys.path.append(REFERENCE_ROOT)
+    spec = importlib.util.spec_from_file_location(
+        "_ref_trimul_autotune", os.path.join(REFERENCE_ROOT, "fold_cp_ops", "workflows", "trimul_autotune.py"))
+    try:
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    except Exception as exc:  # the reference needs its own dependencies to import
+        pytest.skip(f"reference not importable here: {exc}")
+    case = bf16_round_case(make_case(B=2, N=24, D=128, seed=7, bias=bias, mask=mask))
+    ref = mod.trimul_ref(case["x"], direction, case["mask"], **weights_of(case), eps=1e-5)
+    got = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    assert (got - ref).abs().max().item() <= 2e-5 * max(1.0, ref.abs().max().item())
+
+
+def test_mask_reaches_dual_only_and_gate_reads_xn():
+    """Semantics pins of the reference (tests/workflows/test_trimul_autotune.py:648-667): a zero mask
+    zeroes tri (so out = gate * (beta_out . W + b)), and the gate does not depend on the mask."""
+    case = bf16_round_case(make_case(B=1, N=8, D=128, seed=3, bias="all", mask="ones"))
+    w = weights_of(case)
+    full = trimul_stages(case["x"], "outgoing", case["mask"], **w)
+    zero = trimul_stages(case["x"], "outgoing", torch.zeros_like(case["mask"]), **w)
+    assert torch.equal(full["gate"], zero["gate"])
+    assert zero["tri"].abs().max().item() == 0.0
+    assert zero["a"].abs().max().item() == 0.0
+
+
+def test_directions_differ_and_transpose_relation():
+    """tri_incoming(x) == tri_outgoing(x^T): transposing the pair tensor in (i, j) swaps the index
+    the contraction runs over (the output gate stays at its own (i, j), so only tri relates)."""
+    case = bf16_round_case(make_case(B=1, N=8, D=128, seed=5, bias="all", mask="random"))
+    w = weights_of(case)
+    inc = trimul_stages(case["x"], "incoming", case["mask"], **w)
+    out_t = trimul_stages(case["x"].transpose(1, 2).contiguous(), "outgoing",
+                          case["mask"].transpose(1, 2).contiguous(), **w)
+    assert (inc["tri"] - out_t["tri"]).abs().max().item() < 1e-4
+    out = trimul_stages(case["x"], "outgoing", case["mask"], **w)
+    assert (inc["out"] - out["out"]).abs().max().item() > 1e-2
+
+
+def test_bad_direction_raises():
+    case = make_case(B=1, N=8, D=128, seed=1)
+    with pytest.raises(ValueError):
+        trimul_oracle(case["x"], "sideways", None, **weights_of(case))
+
+
+def test_bounds_shapes():
+    ref = torch.randn(4, 4)
+    assert tolerance_bound(ref).shape == ref.shape
+    assert cp1_bound(ref).shape == ref.shape
