@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Benchmark of the fused TriMul forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the README shape of the reference -- z (1, 4096, 4096, 256) bf16 ~ N(0,1), outgoing,
+mask of ones, LayerNorm affine off identity, six projection matrices ~ N(0, 1/D), biases 0,
+seeded -- sharded over a flat 1-D cp mesh with cp = N GPUs (strong scaling: total work fixed).
+Metric: TriMul forward TFLOP/s with FLOPs = 2*B*D*N^3 + 12*B*N^2*D^2.
+
+One JSON line is printed by rank 0.  ``value`` is timed with inputs resident in HBM (CUDA events
+on the launching stream, max over ranks); ``e2e`` times the same forward through the public
+module with pinned-host input and output copies inside the window; ``roofline`` reports the
+dominant kernel (the triangle contraction) against the measured bf16 tensor peak; ``cpu_baseline``
+times the CPU oracle (a port of the reference's eager TriMul) on a bounded sample.
+
+``--impl reference`` times the reference's eager PyTorch TriMul on the host cores (the reference's
+fused kernels are SM90-only and refuse to run on sm_100), on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (B, N, D)
+    "readme_n4096_d256": (1, 4096, 4096, 256),
+    "single_n1024_d128": (1, 1024, 1024, 128),
+    "smoke_n256_d128": (1, 256, 256, 128),
+}
+CPU_SAMPLE_N = 384  # token extent of the bounded CPU sample (same D, same distributions)
+
+
+def flops(B, N, D):
+    return 2.0 * B * D * N ** 3 + 12.0 * B * N * N * D * D
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_layer_weights(D, seed, device):
+    """Seeded weights of the benchmark configuration: gains 1 + 0.1 N, LN biases 0.1 N, projection
+    matrices N(0, 1/D), projection biases absent."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    w = {
+        "norm_in_w": 1 + 0.1 * rn(D), "norm_in_b": 0.1 * rn(D), "norm_out_w": 1 + 0.1 * rn(D), "norm_out_b": 0.1 * rn(D),
+        "p_in_w": rn(2 * D, D) / D ** 0.5, "g_in_w": rn(2 * D, D) / D ** 0.5,
+        "p_out_w": rn(D, D) / D ** 0.5, "g_out_w": rn(D, D) / D ** 0.5,
+        "p_in_b": None, "g_in_b": None, "p_out_b": None, "g_out_b": None,
+    }
+    return {k: (None if v is None else v.to(device)) for k, v in w.items()}
+
+
+def cpu_reference_time(D, direction, threads, n_sample=CPU_SAMPLE_N, reps=2):
+    """Time the CPU oracle (port of the reference's eager fp32 TriMul) at a reduced token extent."""
+    from oracle.trimul_oracle import trimul_oracle
+
+    torch.set_num_threads(threads)
+    w = make_layer_weights(D, 0, "cpu")
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, n_sample, n_sample, D, generator=g)
+    m = torch.ones(1, n_sample, n_sample)
+    trimul_oracle(x[:, :64, :64].contiguous(), direction, m[:, :64, :64].contiguous(), **w)  # warm-up
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        trimul_oracle(x, direction, m, **w)
+        best = min(best, time.perf_counter() - t0)
+    return best, flops(1, n_sample, D) / best / 1e12
+
+
+def run_reference(args):
+    """--impl reference: the reference's eager TriMul (restated in oracle/) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, N, _, D = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    n_sample = CPU_SAMPLE_N
+    from oracle.trimul_oracle import trimul_oracle
+
+    torch.set_num_threads(cores)
+    w = make_layer_weights(D, 0, "cpu")
+    x = torch.randn(1, n_sample, n_sample, D, generator=torch.Generator().manual_seed(1))
+    m = torch.ones(1, n_sample, n_sample)
+    for _ in range(max(1, min(args.warmup, 1))):
+        trimul_oracle(x, args.direction, m, **w)
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        trimul_oracle(x, args.direction, m, **w)
+        times.append(time.perf_counter() - t0)
+    dt = sum(times) / len(times)
+    tf = flops(1, n_sample, D) / dt / 1e12
+    sample = (f"one forward at N={n_sample} (same D={D}, same distributions) per step, "
+              f"{flops(1, n_sample, D):.3e} FLOP; the full N={N} workload is {flops(B, N, D):.3e} FLOP")
+    line = {
+        "impl": "reference", "metric": "trimul_fwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "N": N, "D": D, "direction": args.direction,
+                   "note": "reference fused kernels are SM90-only; its eager PyTorch TriMul timed on host cores"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from torch.distributed.tensor import DTensor, Shard
+
+    from fold_cp_ops_b200.distributed import DistributedManager
+    from fold_cp_ops_b200.distributed.trimul_weights import trimul_module_from_weights
+    from fold_cp_ops_b200.distributed.workflows.trimul_autotuned import TriangularMultiplication
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if "RANK" not in os.environ:  # plain `python bench.py`: a one-rank env:// launch
+        os.environ.update(RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", LOCAL_WORLD_SIZE="1",
+                          MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29500 + os.getpid() % 2000))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    DistributedManager.initialize(device_type="cuda")
+    DistributedManager.init_nvshmem()
+    dm = DistributedManager()
+    rank, cp, dev = dm.rank, dm.world_size, dm.device
+    from collections import OrderedDict
+
+    DistributedManager.create_grid_group(OrderedDict(cp=cp))
+    mesh = dm.device_mesh
+    B, N, _, D = WORKLOADS[args.workload]
+    torch.manual_seed(0)
+    w = make_layer_weights(D, 0, dev)
+    layer = trimul_module_from_weights(w)
+    trimul = TriangularMultiplication(layer, args.direction, mesh if cp > 1 else None, dm, dtype=torch.bfloat16)
+    n_loc = N // cp
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    # pinned host copies: the end-to-end leg moves them every step
+    x_host = torch.empty(B, n_loc, N, D, dtype=torch.bfloat16).pin_memory()
+    chunk = max(1, n_loc // 8)
+    for i0 in range(0, n_loc, chunk):  # fill in slices: a full fp32 randn of the block would not fit comfortably
+        x_host[:, i0:i0 + chunk] = torch.randn(B, min(chunk, n_loc - i0), N, D, generator=gen).to(torch.bfloat16)
+    m_host = torch.ones(B, n_loc, N, dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty(B, n_loc, N, D, dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev, non_blocking=True)
+    m_dev = m_host.to(dev, non_blocking=True)
+
+    def wrap(t, gshape):
+        if cp == 1:
+            return t
+        st = torch.empty(gshape, device="meta").stride()
+        return DTensor.from_local(t, mesh, [Shard(1)], shape=torch.Size(gshape), stride=st, run_check=False)
+
+    x_in, m_in = wrap(x_dev, (B, N, N, D)), wrap(m_dev, (B, N, N))
+    trimul.prepare(n_token=N, batch=B, masked=True)
+
+    def barrier():
+        if cp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        return trimul(x_in, m_in)
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True)
+        md = m_host.to(dev, non_blocking=True)
+        o = trimul(wrap(xd, (B, N, N, D)), wrap(md, (B, N, N)))
+        ol = o.to_local() if cp > 1 else o
+        out_host.copy_(ol, non_blocking=True)
+
+    for _ in range(max(3, args.warmup)):
+        out = step_resident()
+    barrier()
+    # ---- value: inputs resident in HBM ---------------------------------------------------------
+    sampler = ClockSampler(dev.index).start() if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(args.steps):
+        out = step_resident()
+    ev[1].record()
+    barrier()
+    ms = ev[0].elapsed_time(ev[1]) / args.steps
+    clocks = sampler.stop() if sampler else None
+    # ---- per-stage timing of the dominant kernel (live, CUDA events on the launching stream) ----
+    stage_ms = None
+    eng = None
+    if cp == 1:
+        from fold_cp_ops_b200.workflows import trimul_autotune as wf
+        eng = next(reversed(wf._ENGINE_CACHE.values())) if wf._ENGINE_CACHE else None
+    else:
+        eng = next(iter(trimul._engines.values()))
+    if eng is not None:
+        eng.stage_log = True
+        import contextlib
+        import io
+        acc = {}
+        with contextlib.redirect_stdout(io.StringIO()):
+            for _ in range(3):
+                step_resident()
+                for k, v in eng.last_stage_ms.items():
+                    acc.setdefault(k, []).append(v)
+        eng.stage_log = False
+        stage_ms = {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
+    # ---- e2e: pinned host -> device, forward, device -> pinned host, every step -----------------
+    step_e2e()
+    barrier()
+    ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev2[0].record()
+    for _ in range(args.steps):
+        step_e2e()
+    ev2[1].record()
+    barrier()
+    ms_e2e = ev2[0].elapsed_time(ev2[1]) / args.steps
+    # ---- reduce over ranks (max) ----------------------------------------------------------------
+    t = torch.tensor([ms, ms_e2e] + ([stage_ms[k] for k in ("ln_gated_proj", "tri_contract", "ln_out_proj")]
+                                     if stage_ms else [0, 0, 0]), device=dev, dtype=torch.float64)
+    if cp > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e, t_a, t_b, t_c = t.tolist()
+    if eng is not None:
+        eng.check()
+    # ---- parity spot check at full size: a sampled output tile against the oracle --------------
+    verify = None
+    if args.verify and rank == 0:
+        verify = spot_check(trimul, w, x_host, out.to_local() if cp > 1 else out, N, D, n_loc, args.direction)
+    if rank == 0:
+        peaks = measured_peaks()
+        fl = flops(B, N, D)
+        tf = fl / (ms * 1e-3) / 1e12
+        # dominant kernel: the contraction; algorithmic FLOPs per launch = 2*B*(D/cp)*N^3 on each rank
+        fl_b = 2.0 * B * (D / cp) * N ** 3
+        ach = fl_b / (t_b * 1e-3) / 1e12 if t_b > 0 else None
+        peak = peaks["bf16_tflops_sustained"]
+        roof = {"bound": "tensor", "kernel": "tri_contract_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                "frac": (ach / peak) if ach else None, "traffic": None,
+                "peak_source": f"{peaks['source']} (sustained: the kernel runs inside a long step)",
+                "frac_of_burst_peak": (ach / peaks["bf16_tflops"]) if ach else None,
+                "stage_ms": {"ln_gated_proj": t_a, "tri_contract": t_b, "ln_out_proj": t_c}}
+        cpu = None
+        if cp == 1 or True:
+            cores = os.cpu_count() or 1
+            secs, cpu_tf = cpu_reference_time(D, args.direction, cores)
+            cpu = {"value": cpu_tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                   "sample": f"oracle forward at N={CPU_SAMPLE_N}, D={D} (best of 2, {secs:.2f} s each); "
+                             f"FLOPs scale as 2*D*N^3 + 12*N^2*D^2"}
+        bytes_in = x_host.numel() * 2 + m_host.numel() * 2
+        bytes_out = out_host.numel() * 2
+        line = {
+            "metric": "trimul_fwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": cp, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "N": N, "D": D, "direction": args.direction,
+                       "parallelism": f"cp{cp}", "mesh": "1-D, rows sharded", "mask": "ones",
+                       "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed"},
+            "clocks": clocks,
+            "e2e": {"value": fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
+            "gpu_launches": args.steps * (3 if cp == 1 else 3 + 7),
+            "roofline": roof, "cpu_baseline": cpu,
+        }
+        if verify is not None:
+            line["verify"] = verify
+        print(json.dumps(line), flush=True)
+    trimul.free()
+    DistributedManager.cleanup()
+
+
+def spot_check(trimul, w, x_host, out_local, N, D, n_loc, direction, rows=2, cols=64):
+    """Oracle on a (rows x cols) output patch of rank 0's block, from the GLOBAL input.  Only valid
+    at cp=1 (rank 0 holds every token); at cp>1 the multi-GPU tests cover parity."""
+    if n_loc != N:
+        return {"skipped": "cp > 1: rank 0 does not hold the global input"}
+    from oracle.trimul_oracle import layer_norm
+
+    dev = out_local.device
+    wf = {k: (None if v is None else v.float()) for k, v in w.items()}
+    x = x_host.to(dev).float()[0]  # (N, N, D)
+
+    def ab_rows(sel_rows=None, sel_cols=None):
+        xs = x[sel_rows] if sel_rows is not None else x[:, sel_cols].transpose(0, 1)
+        xn = layer_norm(xs, wf["norm_in_w"], wf["norm_in_b"], 1e-5)
+        ab = (xn @ wf["p_in_w"].T) * torch.sigmoid(xn @ wf["g_in_w"].T)
+        return ab[..., :D], ab[..., D:]
+
+    ii = torch.arange(rows, device=dev) * 7 + 3
+    jj = torch.arange(cols, device=dev) * 5 + 1
+    if direction == "outgoing":
+        a, _ = ab_rows(sel_rows=ii)          # (rows, N, D): a[i, k]
+        _, b = ab_rows(sel_rows=jj)          # (cols, N, D): b[j, k]
+    else:
+        a, _ = ab_rows(sel_cols=ii)          # a[k, i] as (rows, N, D)
+        _, b = ab_rows(sel_cols=jj)
+    tri = torch.einsum("ikd,jkd->ijd", a, b)
+    trin = layer_norm(tri, wf["norm_out_w"], wf["norm_out_b"], 1e-5)
+    xn_ij = layer_norm(x[ii][:, jj], wf["norm_in_w"], wf["norm_in_b"], 1e-5)
+    ref = (trin @ wf["p_out_w"].T) * torch.sigmoid(xn_ij @ wf["g_out_w"].T)
+    got = out_local[0][ii][:, jj].float()
+    err = (got - ref).abs()
+    return {"patch": [rows, cols], "max_abs_err": err.max().item(),
+            "max_rel_err": (err / ref.abs().clamp_min(1e-2)).max().item(),
+            "within_2e-2+6e-2|ref|": bool((err <= 2e-2 + 6e-2 * ref.abs()).all().item())}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="readme_n4096_d256")
+    ap.add_argument("--direction", choices=("outgoing", "incoming"), default="outgoing")
+    ap.add_argument("--verify", action="store_true", default=True)
+    ap.add_argument("--no-verify", dest="verify", action="store_false")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

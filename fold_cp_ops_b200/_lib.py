@@ -96,12 +96,11 @@ def load():
         lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, f32p, f32p, vp, f32p, vp, vp, u64, vp]
         lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, f32p, f32p,
                                              vp, f32p, vp, vp, vp, vp, vp, u64, vp]
-        if hasattr(lib, "trimul_sm100_peer_signal"):
-            lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, i32, u64, vp]
-            lib.trimul_sm100_peer_wait.argtypes = [vp, i32, i32, u64, vp, u64, vp]
+        lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, vp]
+        lib.trimul_sm100_peer_wait.argtypes = [vp, i32, u64, vp, u64, vp]
         for name in ("trimul_sm100_query", "trimul_sm100_workspace", "trimul_sm100_pack_weights",
                      "trimul_sm100_ln_gated_proj", "trimul_sm100_tri_contract", "trimul_sm100_ln_out_proj",
-                     "trimul_sm100_forward"):
+                     "trimul_sm100_forward", "trimul_sm100_peer_signal", "trimul_sm100_peer_wait"):
             getattr(lib, name).restype = C.c_int
         _lib = lib
         return lib

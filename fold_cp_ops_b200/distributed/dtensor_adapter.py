@@ -86,3 +86,18 @@ def _ensure_nvshmem(distributed_manager=None) -> None:
     if manager_cls is None or not hasattr(manager_cls, "init_nvshmem"):
         from .distributed_manager import DistributedManager as manager_cls
     manager_cls.init_nvshmem()
+
+
+def _is_rows_sharded_canonical(device_mesh, placements: Sequence) -> bool:
+    """True when the ONLY token axis split over the mesh is the row axis (tensor dim 1): the
+    canonical 1-D layout ``(dp=1, cp0=cp, cp1=1)``."""
+    shape = tuple(device_mesh.mesh.shape)
+    rows = cols = 1
+    for axis, p in enumerate(placements):
+        if _is_shard(p):
+            d = _placement_shard_dim(p)
+            if d == 1:
+                rows *= int(shape[axis])
+            elif d == 2:
+                cols *= int(shape[axis])
+    return rows > 1 and cols == 1

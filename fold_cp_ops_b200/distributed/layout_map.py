@@ -149,7 +149,7 @@ class LayoutRightMap(LayoutMap):
         strides, acc = [], 1
         for n in reversed(shape):
             strides.append(acc)
-            acc *= max(n, 1)
+            acc *= n
         super().__init__(tuple(reversed(strides)), shape)
 
 
@@ -161,5 +161,5 @@ class LayoutLeftMap(LayoutMap):
         strides, acc = [], 1
         for n in shape:
             strides.append(acc)
-            acc *= max(n, 1)
+            acc *= n
         super().__init__(tuple(strides), shape)

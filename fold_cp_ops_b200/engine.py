@@ -1,0 +1,249 @@
+"""The TriMul engine: weights, workspaces and the three-kernel chain for one rank.
+
+Takes over the job of the reference's ``TriMulAutotuned``
+(``fold_cp_ops/distributed/workflows/trimul_autotuned.py:2646-3763``): it owns the packed
+weights, the operand / result buffers (symmetric across the cp group when cp > 1) and runs
+
+    ln_gated_proj  ->  [front flags]  ->  tri_contract  ->  [back flags]  ->  ln_out_proj
+
+on the current CUDA stream.  There is no NCCL call, no host synchronisation and no separate
+all-to-all on that path: the two reshards are the kernels' own epilogue stores into the owning
+rank's buffer, and rank-to-rank ordering is a counter exchange done by two tiny flag kernels.
+At cp=1 the same kernels run with a one-entry peer table and no flag kernels at all.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from . import kernels as K
+
+_LN_KEYS = ("norm_in_w", "norm_in_b", "norm_out_w", "norm_out_b")
+SUPPORTED_D = (128, 256)
+
+
+def _timeout_ns() -> int:
+    ms = os.environ.get("CPO_A2A_WAIT_TIMEOUT_MS")
+    return int(float(ms) * 1e6) if ms else K.DEFAULT_TIMEOUT_NS
+
+
+@dataclass
+class CpGeometry:
+    """How the (N, N) token grid is split over the cp group and where this rank sits.
+
+    ``cp0`` splits rows (tensor dim 1), ``cp1`` columns (tensor dim 2); ``rank`` is this rank's
+    index in row-major (row block, column block) order; ``peers[r]`` is the global rank of the
+    member at that index."""
+
+    cp0: int = 1
+    cp1: int = 1
+    rank: int = 0
+    peers: Tuple[int, ...] = (0,)
+
+    @property
+    def cp(self) -> int:
+        return self.cp0 * self.cp1
+
+
+class PackedWeights:
+    """Device-resident weights in the form the kernels read (built once per layer).
+
+    LayerNorm gains / biases and projection biases stay fp32; the six projection matrices are
+    bf16; the three input-side matrices are regrouped into the five chunk order of
+    ``trimul_sm100_pack_weights``."""
+
+    def __init__(self, w: Dict[str, Optional[torch.Tensor]], device: torch.device):
+        D = int(w["norm_in_w"].shape[0])
+        if D not in SUPPORTED_D:
+            raise ValueError(f"feature width D={D} is not supported by the sm_100a kernels (supported: {SUPPORTED_D})")
+        for key, shape in (("p_in_w", (2 * D, D)), ("g_in_w", (2 * D, D)), ("p_out_w", (D, D)), ("g_out_w", (D, D))):
+            if tuple(w[key].shape) != shape:
+                raise ValueError(f"{key} must be {shape}; got {tuple(w[key].shape)}")
+        self.D = D
+        f32 = lambda t: None if t is None else t.detach().to(device=device, dtype=torch.float32).contiguous()
+        b16 = lambda t: t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
+        self.norm_in_w, self.norm_in_b = f32(w["norm_in_w"]), f32(w.get("norm_in_b"))
+        self.norm_out_w, self.norm_out_b = f32(w["norm_out_w"]), f32(w.get("norm_out_b"))
+        self.p_out_w = b16(w["p_out_w"])
+        self.p_out_b = f32(w.get("p_out_b"))
+        self.w_packed, self.bias_packed = K.pack_weights(
+            D, b16(w["p_in_w"]), b16(w["g_in_w"]), b16(w["g_out_w"]), f32(w.get("p_in_b")), f32(w.get("g_in_b")),
+            f32(w.get("g_out_b")))
+
+
+class TriMulEngine:
+    """One rank's fused TriMul forward.
+
+    ``forward(x_local, direction, mask_local)`` takes this rank's ``(B, N/cp0, N/cp1, D)`` block
+    and returns the same block of the output, freshly allocated, bf16.  Workspaces are cached per
+    ``(B, N)``; at cp > 1 they are symmetric allocations exchanged once with the peers.
+    """
+
+    def __init__(self, w: Dict[str, Optional[torch.Tensor]], *, device: torch.device, eps: float = 1e-5,
+                 geometry: Optional[CpGeometry] = None, process_group=None, recv_cache: Optional[int] = None):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("TriMulEngine needs a CUDA device: the TriMul kernels have no CPU path")
+        K.device_caps(self.device.index if self.device.index is not None else torch.cuda.current_device())
+        with torch.cuda.device(self.device):
+            self.weights = PackedWeights(w, self.device)
+        self.D = self.weights.D
+        self.eps = float(eps)
+        self.geometry = geometry or CpGeometry()
+        self.group = process_group
+        if self.geometry.cp > 1 and process_group is None:
+            raise ValueError("a cp > 1 engine needs the process group of its cp peers")
+        self.status = K.new_status(self.device)
+        self.timeout_ns = _timeout_ns()
+        cap = os.environ.get("CPO_TRIMUL_RECV_CACHE")
+        self._cache_cap = int(cap) if cap else (recv_cache if recv_cache is not None else 2)
+        self._ws: Dict[Tuple[int, int], "_Workspace"] = {}
+        self._epoch = 0
+        self.stage_log = bool(int(os.environ.get("CPO_TRIMUL_STAGE_LOG", "0") or 0))
+        self.last_stage_ms: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _check_shapes(self, x_local: torch.Tensor, N: int) -> None:
+        g = self.geometry
+        cp = g.cp
+        if self.D % cp != 0:
+            raise ValueError(f"D={self.D} must be divisible by cp={cp}")
+        if N % g.cp0 != 0 or N % g.cp1 != 0:
+            raise ValueError(f"N={N} must be divisible by each cp axis {(g.cp0, g.cp1)}")
+        if N % 8 != 0:
+            raise ValueError(f"N must be 16-byte aligned (N % 8 == 0 for a 16-bit activation); got N={N}")
+        if cp > 1 and ((N // g.cp0) % 8 != 0 or (N // g.cp1) % 8 != 0):
+            raise ValueError(f"local token extents {(N // g.cp0, N // g.cp1)} must be multiples of 8")
+        want = (N // g.cp0, N // g.cp1, self.D)
+        if tuple(x_local.shape[1:]) != want:
+            raise ValueError(f"x_local must be (B, {want[0]}, {want[1]}, {want[2]}); got {tuple(x_local.shape)}")
+
+    def _workspace(self, B: int, N: int) -> "_Workspace":
+        key = (B, N)
+        ws = self._ws.get(key)
+        if ws is None:
+            while len(self._ws) >= max(1, self._cache_cap):
+                self._ws.pop(next(iter(self._ws)))  # FIFO; buffers return to their pool by refcount
+            ws = _Workspace(self, B, N)
+            self._ws[key] = ws
+        return ws
+
+    def prepare(self, B: int, N: int) -> None:
+        """Allocate (and, at cp > 1, exchange) the buffers for this shape ahead of the first forward."""
+        with torch.cuda.device(self.device):
+            self._workspace(int(B), int(N))
+
+    @torch.no_grad()
+    def forward(self, x_local: torch.Tensor, direction: str, mask_local: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if direction not in ("outgoing", "incoming"):
+            raise ValueError(f"direction must be 'outgoing' or 'incoming'; got {direction!r}")
+        if x_local.dim() != 4:
+            raise ValueError(f"x_local must be (B, N_i, N_j, D); got {tuple(x_local.shape)}")
+        g = self.geometry
+        B = int(x_local.shape[0])
+        N = int(x_local.shape[1]) * g.cp0
+        self._check_shapes(x_local, N)
+        if x_local.device != self.device:
+            raise ValueError(f"x_local is on {x_local.device}, the engine on {self.device}")
+        x = x_local if x_local.dtype is torch.bfloat16 else x_local.to(torch.bfloat16)
+        x = x.contiguous()
+        mask = None
+        if mask_local is not None:
+            if tuple(mask_local.shape) != tuple(x.shape[:3]) and mask_local.numel() != x.shape[0] * x.shape[1] * x.shape[2]:
+                raise ValueError(f"mask must be {tuple(x.shape[:3])}; got {tuple(mask_local.shape)}")
+            mask = mask_local
+            if mask.dtype not in (torch.bfloat16, torch.float32, torch.uint8, torch.bool):
+                mask = mask.to(torch.float32)
+            mask = mask.contiguous()
+        with torch.cuda.device(self.device):
+            ws = self._workspace(B, N)
+            out = torch.empty_like(x)
+            ws.run(x, mask, direction, out)
+        return out
+
+    def check(self) -> None:
+        """Synchronising check of the device status record (raises on an expired wait)."""
+        K.check_status(self.status)
+
+    def free(self) -> None:
+        """Drop the cached workspaces.  Symmetric blocks go back to their pool by refcount; no
+        collective runs here, so ranks may call this in any order."""
+        self._ws.clear()
+
+
+class _Workspace:
+    """Buffers for one ``(B, N)``.  cp=1: plain allocations, optionally one batch plane at a time
+    when the full-batch operand buffer would not fit; cp>1: symmetric allocations + flag pads."""
+
+    def __init__(self, eng: TriMulEngine, B: int, N: int):
+        self.eng, self.B, self.N = eng, B, N
+        g = eng.geometry
+        D = eng.D
+        dev = eng.device
+        self.ni, self.nj = N // g.cp0, N // g.cp1
+        self.planes_b = B  # batch planes handled per kernel launch
+        if g.cp == 1:
+            geom = K.make_geom(B, N, D, "outgoing", eng.eps)
+            need = K.workspace_bytes(geom)
+            total = need.ab_bytes + need.tri_bytes + need.gate_bytes
+            free, _ = torch.cuda.mem_get_info(dev)
+            budget = int(os.environ.get("CPO_TRIMUL_WORKSPACE_BYTES", 0)) or int(free * 0.9)
+            if B > 1 and total + 2 * B * N * N * D > budget:
+                self.planes_b = 1
+            pb = self.planes_b
+            self.ab = torch.empty((2, D, pb, N, N), dtype=torch.bfloat16, device=dev)
+            self.tri = torch.empty((D, pb, N, N), dtype=torch.bfloat16, device=dev)
+            self.gate = torch.empty((pb, N, N, D), dtype=torch.bfloat16, device=dev)
+            self.ab_ptrs = [self.ab.data_ptr()]
+            self.tri_ptrs = [self.tri.data_ptr()]
+            self.flags = None
+        else:
+            from .distributed import symmetric
+
+            d_loc = D // g.cp
+            self.sym = symmetric.SymmetricWorkspace(
+                eng.group, dev, g, ab_shape=(2, d_loc, B, N, N), tri_shape=(D, B, self.ni, self.nj),
+                status=eng.status, timeout_ns=eng.timeout_ns)
+            self.ab, self.tri = self.sym.ab, self.sym.tri
+            self.ab_ptrs, self.tri_ptrs = self.sym.ab_ptrs, self.sym.tri_ptrs
+            self.gate = torch.empty((B, self.ni, self.nj, D), dtype=torch.bfloat16, device=dev)
+            self.flags = self.sym.flags
+
+    def run(self, x, mask, direction, out) -> None:
+        eng = self.eng
+        g = eng.geometry
+        W = eng.weights
+        pb = self.planes_b
+        log = eng.stage_log
+        for b0 in range(0, self.B, pb):
+            xs = x[b0:b0 + pb]
+            ms = None if mask is None else mask.reshape(self.B, self.ni, self.nj)[b0:b0 + pb]
+            os_ = out[b0:b0 + pb]
+            geom = K.make_geom(pb, self.N, eng.D, direction, eng.eps, g.cp0, g.cp1, g.rank)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if log else None
+            if log:
+                ev[0].record()
+            K.ln_gated_proj(geom, xs, ms, W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed, self.ab_ptrs, self.gate,
+                            eng.status, eng.timeout_ns)
+            if self.flags is not None:
+                self.flags.front_done()
+            if log:
+                ev[1].record()
+            K.tri_contract(geom, self.ab, self.tri_ptrs, eng.status, eng.timeout_ns)
+            if self.flags is not None:
+                self.flags.back_done()
+            if log:
+                ev[2].record()
+            K.ln_out_proj(geom, self.tri, self.gate, W.norm_out_w, W.norm_out_b, W.p_out_w, W.p_out_b, os_,
+                          eng.status, eng.timeout_ns)
+            if self.flags is not None:
+                self.flags.consumed()
+            if log:
+                ev[3].record()
+                ev[3].synchronize()
+                eng.last_stage_ms = {"ln_gated_proj": ev[0].elapsed_time(ev[1]), "tri_contract": ev[1].elapsed_time(ev[2]),
+                                     "ln_out_proj": ev[2].elapsed_time(ev[3])}
+                print(f"[trimul stage log] {eng.last_stage_ms}", flush=True)

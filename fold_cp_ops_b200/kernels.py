@@ -166,3 +166,16 @@ def forward_single(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, ln_ou
                                           _ptr(w_out), _ptr(bias_out), _ptr(ab), _ptr(tri), _ptr(gate), _ptr(out),
                                           _ptr(status), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_forward")
+
+
+def peer_signal(flag_peer_ptrs: Sequence[int], slot: int) -> None:
+    """Add 1 to counter ``slot`` on every rank of the cp group (enqueued on the current stream)."""
+    rc = _lib.load().trimul_sm100_peer_signal(_ptr_array(flag_peer_ptrs), len(flag_peer_ptrs), int(slot), _stream())
+    _lib.check(rc, "trimul_sm100_peer_signal")
+
+
+def peer_wait(local_flags: torch.Tensor, slot: int, expected: int, status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    """Hold the current stream until this rank's counter ``slot`` reaches ``expected`` (bounded)."""
+    rc = _lib.load().trimul_sm100_peer_wait(_ptr(local_flags), int(slot), int(expected), _ptr(status),
+                                            int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_peer_wait")

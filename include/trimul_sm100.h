@@ -135,6 +135,17 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
                          const void* w_out, const float* bias_out, void* ab, void* tri, void* gate, void* out,
                          trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
 
+/* Rank-to-rank ordering of the fused reshards.  Every rank owns a symmetric array of 16 uint64
+ * counters (zeroed once).  `peer_signal` adds 1 to counter `slot` on every rank listed in
+ * flag_peers[0..cp) (release, system scope) and is enqueued after the kernel whose stores it
+ * publishes; `peer_wait` is enqueued before the kernel that consumes them and polls this rank's
+ * own counter until it reaches `expected`, giving up after timeout_ns with a status record.
+ * Replaces `_A2ADeviceSignal` and the `quiet` + `barrier_all` drains
+ * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:322-560, 3272-3300). */
+int trimul_sm100_peer_signal(void* const* flag_peers, int32_t cp, int32_t slot, trimul_stream_t stream);
+int trimul_sm100_peer_wait(const void* local_flags, int32_t slot, uint64_t expected, trimul_status_t* status,
+                           uint64_t timeout_ns, trimul_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,319 @@
+"""Parity of the sm_100a TriMul path against the CPU oracle -- every test calls through the C ABI.
+
+Tolerances (bf16 storage at four points of the chain, fp32 accumulation and statistics):
+  * whole forward vs the fp32 oracle: the reference's cp=1 gate ``0.01*max|ref| + 0.01*|ref|``
+    per element (tests/workflows/test_trimul_autotune.py:78-92 of the reference) AND its
+    distributed gate ``2e-2 + 6e-2*|ref|`` (tests/distributed/workflows/test_trimul_autotuned.py:556);
+  * single kernels vs the oracle with bf16 rounding applied at the same points: a few bf16 ulps.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle.trimul_oracle import (bf16_round_case, cp1_bound, layer_norm, make_case, tolerance_bound, trimul_oracle,
+                                  trimul_stages, weights_of)
+from tests.golden.make_golden import CASES
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _engine(case, eps=1e-5):
+    from fold_cp_ops_b200.engine import TriMulEngine
+
+    return TriMulEngine(weights_of(case), device=torch.device(DEV), eps=eps)
+
+
+def _run(case, direction, *, x_dtype=torch.bfloat16, mask_dtype=torch.float32):
+    eng = _engine(case)
+    x = case["x"].to(DEV).to(x_dtype)
+    m = None if case["mask"] is None else case["mask"].to(DEV).to(mask_dtype)
+    out = eng.forward(x, direction, m)
+    torch.cuda.synchronize()
+    eng.check()
+    return out.float().cpu()
+
+
+def _assert_parity(got, ref, what=""):
+    err = (got - ref).abs()
+    b1, b2 = cp1_bound(ref), tolerance_bound(ref)
+    v1, v2 = int((err > b1).sum()), int((err > b2).sum())
+    rel = (err / ref.abs().clamp_min(1e-3)).max().item()
+    assert not torch.isnan(got).any(), f"{what}: NaN in output"
+    assert v1 == 0 and v2 == 0, (f"{what}: {v1} elements beyond the cp=1 bound, {v2} beyond the distributed bound; "
+                                 f"max|err|={err.max().item():.5f} max rel={rel:.4f} max|ref|={ref.abs().max().item():.4f}")
+
+
+# ------------------------------------------------------------------------------------------------
+# golden vectors of the reference's own trimul_ref
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_forward_matches_reference_golden(name, golden):
+    kw = dict(CASES[name])
+    direction = kw.pop("direction")
+    case = bf16_round_case(make_case(**kw))
+    got = _run(case, direction)
+    _assert_parity(got, torch.from_numpy(golden[name]), name)
+
+
+# ------------------------------------------------------------------------------------------------
+# oracle on seeded inputs: directions x bias x mask x shapes (edge shapes included)
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("B,N,D,bias,mask", [
+    (1, 8, 128, "none", "none"),        # smallest legal token extent
+    (1, 72, 128, "all", "random"),      # not a multiple of any tile
+    (2, 136, 128, "out", "pad"),        # batch > 1, ragged tiles, padding mask
+    (1, 200, 256, "all", "ones"),       # D=256, ragged
+    (2, 64, 256, "none", "random"),
+    (1, 256, 128, "all", "random"),     # the reference's own parity shape (N=256, D=128)
+])
+def test_forward_matches_oracle(direction, B, N, D, bias, mask):
+    case = bf16_round_case(make_case(B, N, D, seed=1000 + N + D, bias=bias, mask=mask))
+    ref = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    _assert_parity(_run(case, direction), ref, f"{direction} B{B} N{N} D{D} {bias} {mask}")
+
+
+def test_reference_cpu_config_shape():
+    """configs[0] of the benchmark definition: (1,256,256,128), gamma=1, beta=0, biases 0, mask ones."""
+    case = bf16_round_case(make_case(1, 256, 128, seed=0, ln_affine=False, bias="none", mask="ones"))
+    ref = trimul_oracle(case["x"], "outgoing", case["mask"], **weights_of(case))
+    _assert_parity(_run(case, "outgoing"), ref, "config0")
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_single_gpu_config_shape_against_gpu_evaluated_oracle(direction):
+    """configs[1]: (1,1024,1024,128) with LayerNorm affine and biases on all six projections.  The
+    fp32 oracle at this size is evaluated by the same oracle code on CUDA fp32 tensors (TF32 off)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    case = bf16_round_case(make_case(1, 1024, 128, seed=1, bias="all", mask="ones"))
+    cg = {k: (None if v is None else v.to(DEV)) for k, v in case.items()}
+    ref = trimul_oracle(cg["x"], direction, cg["mask"], **{k: cg[k] for k in weights_of(case)}).cpu()
+    del cg
+    torch.cuda.empty_cache()
+    _assert_parity(_run(case, direction), ref, f"config1 {direction}")
+
+
+def test_off_centre_rows():
+    """Rows whose mean is far from zero (|mean| >> std) must not lose the LayerNorm signal
+    (the reference pins this for its own chains: tests/workflows/test_trimul_autotune.py:611-633)."""
+    case = make_case(1, 64, 128, seed=9, bias="all", mask="none")
+    case["x"] = case["x"] + 40.0 * torch.randn(1, 64, 64, 1, generator=torch.Generator().manual_seed(4))
+    case = bf16_round_case(case)
+    ref = trimul_oracle(case["x"], "outgoing", None, **weights_of(case))
+    _assert_parity(_run(case, "outgoing"), ref, "off-centre")
+
+
+# ------------------------------------------------------------------------------------------------
+# size-independent properties (also used at full benchmark sizes by bench.py --verify)
+# ------------------------------------------------------------------------------------------------
+def test_deterministic_and_mask_of_ones_is_identity():
+    case = bf16_round_case(make_case(1, 128, 128, seed=5, bias="all", mask="ones"))
+    a = _run(case, "outgoing")
+    b = _run(case, "outgoing")
+    assert torch.equal(a, b)
+    nomask = dict(case, mask=None)
+    assert torch.equal(a, _run(nomask, "outgoing"))
+    for dt in (torch.bfloat16, torch.bool, torch.uint8):
+        assert torch.equal(a, _run(case, "outgoing", mask_dtype=dt))
+
+
+def test_batch_planes_are_independent():
+    case = bf16_round_case(make_case(2, 96, 128, seed=6, bias="all", mask="random"))
+    both = _run(case, "incoming")
+    for b in range(2):
+        one = dict(case, x=case["x"][b:b + 1].contiguous(), mask=case["mask"][b:b + 1].contiguous())
+        assert torch.equal(both[b:b + 1], _run(one, "incoming"))
+
+
+def test_zero_mask_kills_the_contraction_only():
+    """mask = 0 zeroes a|b, hence tri; the output is then gate * (beta_out . W^T + b), with the gate
+    untouched by the mask."""
+    case = bf16_round_case(make_case(1, 64, 128, seed=7, bias="all", mask="ones"))
+    case["mask"] = torch.zeros_like(case["mask"])
+    ref = trimul_oracle(case["x"], "outgoing", case["mask"], **weights_of(case))
+    assert ref.abs().max() > 1e-3
+    _assert_parity(_run(case, "outgoing"), ref, "zero mask")
+
+
+def test_incoming_is_outgoing_of_the_transposed_pair_tensor():
+    """tri_in(x) == tri_out(x^T): checked on the contraction kernel's operand planes and output."""
+    from fold_cp_ops_b200 import kernels as K
+
+    B, N, D = 1, 96, 128
+    case = bf16_round_case(make_case(B, N, D, seed=8, bias="all", mask="random"))
+    eng = _engine(case)
+    W = eng.weights
+
+    def planes(x, m, direction):
+        ab = torch.empty((2, D, B, N, N), dtype=torch.bfloat16, device=DEV)
+        gate = torch.empty((B, N, N, D), dtype=torch.bfloat16, device=DEV)
+        tri = torch.empty((D, B, N, N), dtype=torch.bfloat16, device=DEV)
+        g = K.make_geom(B, N, D, direction, 1e-5)
+        K.ln_gated_proj(g, x, m, W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed, [ab.data_ptr()], gate, eng.status)
+        K.tri_contract(g, ab, [tri.data_ptr()], eng.status)
+        torch.cuda.synchronize()
+        return ab.cpu(), tri.cpu()
+
+    x = case["x"].to(DEV).bfloat16()
+    m = case["mask"].to(DEV)
+    ab_in, tri_in = planes(x, m, "incoming")
+    ab_out, tri_out = planes(x.transpose(1, 2).contiguous(), m.transpose(1, 2).contiguous(), "outgoing")
+    assert torch.equal(ab_in, ab_out)
+    assert torch.equal(tri_in, tri_out)
+    eng.check()
+
+
+# ------------------------------------------------------------------------------------------------
+# single kernels against the oracle with bf16 rounding at the same points
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("D,N,B", [(128, 72, 1), (256, 40, 2)])
+def test_kernel_ln_gated_proj(direction, D, N, B):
+    from fold_cp_ops_b200 import kernels as K
+
+    case = bf16_round_case(make_case(B, N, D, seed=11, bias="all", mask="random"))
+    eng = _engine(case)
+    W = eng.weights
+    ab = torch.full((2, D, B, N, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gate = torch.full((B, N, N, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    g = K.make_geom(B, N, D, direction, 1e-5)
+    K.ln_gated_proj(g, case["x"].to(DEV).bfloat16(), case["mask"].to(DEV), W.norm_in_w, W.norm_in_b, W.w_packed,
+                    W.bias_packed, [ab.data_ptr()], gate, eng.status)
+    torch.cuda.synchronize()
+    eng.check()
+    s = trimul_stages(case["x"], direction, case["mask"], **weights_of(case), round_bf16=True)
+    for h, key in ((0, "a"), (1, "b")):
+        want = s[key].permute(3, 0, 1, 2)
+        if direction == "incoming":
+            want = want.transpose(2, 3)
+        err = (ab[h].float().cpu() - want).abs()
+        assert (err <= 0.02 + 0.02 * want.abs()).all(), (key, err.max().item())
+    err = (gate.float().cpu() - s["gate"]).abs()
+    assert (err <= 0.01).all(), err.max().item()
+
+
+@pytest.mark.parametrize("N,planes_d", [(8, 128), (64, 128), (200, 128), (1024, 128)])
+def test_kernel_tri_contract(N, planes_d):
+    from fold_cp_ops_b200 import kernels as K
+
+    torch.manual_seed(N)
+    D, B = planes_d, 1
+    ab = (0.5 * torch.randn(2, D, B, N, N, device=DEV)).to(torch.bfloat16)
+    tri = torch.full((D, B, N, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    st = K.new_status(DEV)
+    K.tri_contract(K.make_geom(B, N, D, "outgoing", 1e-5), ab, [tri.data_ptr()], st)
+    torch.cuda.synchronize()
+    K.check_status(st)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    want = torch.bmm(ab[0, :, 0].float(), ab[1, :, 0].float().transpose(1, 2))
+    err = (tri[:, 0].float() - want).abs()
+    # fp32 accumulation of exact bf16 products, one bf16 rounding of the result
+    assert (err <= 2.0 ** -8 * want.abs() + 1e-3 * want.abs().max()).all(), err.max().item()
+
+
+@pytest.mark.parametrize("D,B,n", [(128, 1, 8), (128, 1, 72), (256, 2, 40)])
+def test_kernel_ln_out_proj(D, B, n):
+    from fold_cp_ops_b200 import kernels as K
+
+    rows = B * n * n
+    torch.manual_seed(rows)
+    tri = (3.0 * torch.randn(D, rows, device=DEV) + 0.5).to(torch.bfloat16)
+    gate = torch.rand(rows, D, device=DEV).to(torch.bfloat16)
+    lw = (1 + 0.1 * torch.randn(D, device=DEV)).float()
+    lb = (0.1 * torch.randn(D, device=DEV)).float()
+    w = (torch.randn(D, D, device=DEV) / D ** 0.5).to(torch.bfloat16)
+    bo = (0.02 * torch.randn(D, device=DEV)).float()
+    out = torch.full((rows, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    st = K.new_status(DEV)
+    K.ln_out_proj(K.make_geom(B, n, D, "outgoing", 1e-5), tri, gate, lw, lb, w, bo, out, st)
+    torch.cuda.synchronize()
+    K.check_status(st)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    trin = layer_norm(tri.float().t(), lw, lb, 1e-5).to(torch.bfloat16).float()
+    want = (trin @ w.float().t() + bo) * gate.float()
+    err = (out.float() - want).abs()
+    assert (err <= 0.03 + 0.02 * want.abs()).all(), err.max().item()
+
+
+# ------------------------------------------------------------------------------------------------
+# the single-GPU front doors and their refusals
+# ------------------------------------------------------------------------------------------------
+def test_trimul_autotuned_front_door_and_dtype_roundtrip():
+    from fold_cp_ops_b200.workflows.trimul_autotune import trimul_autotuned
+
+    case = bf16_round_case(make_case(1, 64, 128, seed=12, bias="all", mask="random"))
+    w = {k: (None if v is None else v.to(DEV)) for k, v in weights_of(case).items()}
+    ref = trimul_oracle(case["x"], "incoming", case["mask"], **weights_of(case))
+    for dt in (torch.bfloat16, torch.float32):
+        x = case["x"].to(DEV).to(dt)
+        got = trimul_autotuned(x, **w, mask=case["mask"].to(DEV), direction="incoming")
+        assert got.dtype is dt and got.shape == x.shape
+        _assert_parity(got.float().cpu(), ref, f"front door {dt}")
+    buf = torch.empty_like(x)
+    assert trimul_autotuned(x, **w, direction="incoming", out=buf) is buf
+
+
+def test_refusals():
+    from fold_cp_ops_b200.workflows.trimul_autotune import trimul_autotuned
+
+    case = make_case(1, 16, 128, seed=13)
+    w = {k: (None if v is None else v.to(DEV)) for k, v in weights_of(case).items()}
+    x = case["x"].to(DEV).bfloat16()
+    with pytest.raises(ValueError, match="direction"):
+        trimul_autotuned(x, **w, direction="sideways")
+    with pytest.raises(ValueError, match="select"):
+        trimul_autotuned(x, **w, select="fastest")
+    with pytest.raises(ValueError, match="16-byte aligned"):
+        trimul_autotuned(x[:, :12, :12].contiguous(), **w)
+    with pytest.raises(ValueError, match="square"):
+        trimul_autotuned(x[:, :8].contiguous(), **w)
+    with pytest.raises(ValueError, match="float32"):
+        trimul_autotuned(x, **dict(w, norm_in_w=w["norm_in_w"].bfloat16()))
+    with pytest.raises(ValueError, match=r"\(2D, D\)"):
+        trimul_autotuned(x, **dict(w, p_in_w=w["p_in_w"][:128]))
+    with pytest.raises(ValueError, match="mask"):
+        trimul_autotuned(x, **w, mask=torch.ones(1, 8, 8, device=DEV))
+    case64 = make_case(1, 16, 64, seed=14)
+    w64 = {k: (None if v is None else v.to(DEV)) for k, v in weights_of(case64).items()}
+    with pytest.raises(ValueError, match="not supported"):
+        trimul_autotuned(case64["x"].to(DEV).bfloat16(), **w64)
+
+
+def test_module_front_door_cp1_plain_tensor_and_one_device_mesh():
+    import torch.nn as nn
+
+    from fold_cp_ops_b200.distributed.trimul_weights import trimul_module_from_weights
+    from fold_cp_ops_b200.distributed.workflows.trimul_autotuned import TriangularMultiplication
+
+    case = bf16_round_case(make_case(1, 64, 128, seed=15, bias="out", mask="random"))
+    layer = trimul_module_from_weights({k: (None if v is None else v.to(DEV)) for k, v in weights_of(case).items()})
+    mod = TriangularMultiplication(layer, "outgoing", None, None)
+    assert mod.incoming_variant == "cp1_fallback" and mod.prepare(n_token=64) is None
+    x = case["x"].to(DEV).bfloat16()
+    got = mod(x, case["mask"].to(DEV))
+    assert isinstance(got, torch.Tensor) and got.dtype is torch.bfloat16
+    ref = trimul_oracle(case["x"], "outgoing", case["mask"], **weights_of(case))
+    _assert_parity(got.float().cpu(), ref, "module cp1")
+    mod.free()
+
+
+# ------------------------------------------------------------------------------------------------
+# bounded waits: a wait that nothing satisfies ends with a status, not a hang
+# ------------------------------------------------------------------------------------------------
+def test_expired_wait_reports_status_and_context_survives():
+    from fold_cp_ops_b200 import kernels as K
+
+    flags = torch.zeros(16, dtype=torch.int64, device=DEV)
+    st = K.new_status(DEV)
+    K.peer_wait(flags, 3, 1, st, timeout_ns=20_000_000)  # 20 ms; nobody signals slot 3
+    torch.cuda.synchronize()
+    with pytest.raises(K.DeviceWaitTimeout, match="peer_sync"):
+        K.check_status(st)
+    # the status was cleared and the context still works: a satisfied wait passes
+    K.peer_signal([flags.data_ptr()], 3)
+    K.peer_wait(flags, 3, 1, st, timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    K.check_status(st)
+    assert int(flags[3].item()) == 1
