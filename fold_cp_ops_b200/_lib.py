@@ -28,6 +28,7 @@ MAX_PEERS = 8
 EXPORTED_SYMBOLS = (
     "trimul_sm100_query",
     "trimul_sm100_workspace",
+    "trimul_sm100_reshard_plan",
     "trimul_sm100_last_error",
     "trimul_sm100_pack_weights",
     "trimul_sm100_ln_gated_proj",
@@ -51,6 +52,13 @@ class Geom(C.Structure):
 
 class Workspace(C.Structure):
     _fields_ = [("ab_bytes", C.c_uint64), ("tri_bytes", C.c_uint64), ("gate_bytes", C.c_uint64)]
+
+
+class ReshardPlan(C.Structure):
+    _fields_ = [("n_lines", C.c_int32), ("n_walk", C.c_int32), ("batch_rows", C.c_int64), ("line_rows", C.c_int64),
+                ("walk_rows", C.c_int64), ("plane_elems", C.c_int64), ("dst_base", C.c_int64), ("dst_line", C.c_int64),
+                ("d_loc", C.c_int32), ("planes", C.c_int32), ("ni_loc", C.c_int32), ("nj_loc", C.c_int32),
+                ("chan_offset", C.c_int32), ("pad", C.c_int32), ("rows", C.c_int64)]
 
 
 class TrimulLibraryError(RuntimeError):
@@ -89,6 +97,8 @@ def load():
         lib.trimul_sm100_last_error.argtypes = []
         lib.trimul_sm100_query.argtypes = [C.c_int, C.POINTER(Caps)]
         lib.trimul_sm100_workspace.argtypes = [C.POINTER(Geom), C.POINTER(Workspace)]
+        lib.trimul_sm100_reshard_plan.argtypes = [C.POINTER(Geom), C.POINTER(ReshardPlan)]
+        lib.trimul_sm100_reshard_plan.restype = C.c_int
         lib.trimul_sm100_pack_weights.argtypes = [i32, vp, vp, vp, f32p, f32p, f32p, vp, f32p, vp]
         lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p,
                                                    C.POINTER(vp), vp, vp, u64, vp]

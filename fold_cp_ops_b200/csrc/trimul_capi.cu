@@ -117,6 +117,45 @@ int check_geom(const trimul_geom_t* g, Derived* d) {
   return TRIMUL_OK;
 }
 
+
+// Where this rank's tokens go in the front reshard and where contraction tiles go in the back one.
+void derive_plan(const trimul_geom_t* g, const Derived& d, trimul_reshard_plan_t* p) {
+  const long n = g->n;
+  p->batch_rows = static_cast<long>(d.ni_loc) * d.nj_loc;
+  if (g->direction == TRIMUL_OUTGOING) {
+    if (g->cp1 == 1) {
+      // rows (b, i, :) are contiguous in x and in the destination plane: walk the whole block
+      p->n_lines = 1;
+      p->n_walk = static_cast<int32_t>(static_cast<long>(d.ni_loc) * d.nj_loc);
+      p->line_rows = 0;
+      p->walk_rows = 1;
+      p->dst_base = d.i_off * n;
+      p->dst_line = 0;
+    } else {
+      p->n_lines = d.ni_loc;
+      p->n_walk = d.nj_loc;
+      p->line_rows = d.nj_loc;
+      p->walk_rows = 1;
+      p->dst_base = d.i_off * n + d.j_off;
+      p->dst_line = n;
+    }
+  } else {
+    p->n_lines = d.nj_loc;
+    p->n_walk = d.ni_loc;
+    p->line_rows = 1;
+    p->walk_rows = d.nj_loc;
+    p->dst_base = d.j_off * n + d.i_off;
+    p->dst_line = n;
+  }
+  p->plane_elems = n * n;
+  p->d_loc = d.d_loc;
+  p->planes = d.d_loc * g->batch;
+  p->ni_loc = d.ni_loc;
+  p->nj_loc = d.nj_loc;
+  p->chan_offset = g->rank * d.d_loc;
+  p->rows = d.rows;
+}
+
 // ---------------------------------------------------------------------------------------------
 // weight packing kernel (runs once per layer)
 // ---------------------------------------------------------------------------------------------
@@ -178,6 +217,15 @@ int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out) {
   return TRIMUL_OK;
 }
 
+int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* out) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan is NULL");
+  derive_plan(geom, d, out);
+  return TRIMUL_OK;
+}
+
 int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
                               const float* p_in_b, const float* g_in_b, const float* g_out_b, void* w_packed,
                               float* bias_packed, trimul_stream_t stream) {
@@ -224,41 +272,23 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   a.eps = geom->eps;
   a.D = D;
   a.batch = geom->batch;
-  a.batch_rows = static_cast<long>(d.ni_loc) * d.nj_loc;
-  const long n = geom->n;
-  if (geom->direction == TRIMUL_OUTGOING) {
-    if (geom->cp1 == 1) {
-      // rows (b, i, :) are contiguous in x and in the destination plane: walk the whole block
-      a.n_lines = 1;
-      a.n_walk = static_cast<int>(static_cast<long>(d.ni_loc) * d.nj_loc);
-      a.line_rows = 0;
-      a.walk_rows = 1;
-      a.dst_base = d.i_off * n;
-      a.dst_line = 0;
-      if (static_cast<long>(d.ni_loc) * d.nj_loc > 0x7fffffffL)
-        return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token block too large");
-    } else {
-      a.n_lines = d.ni_loc;
-      a.n_walk = d.nj_loc;
-      a.line_rows = d.nj_loc;
-      a.walk_rows = 1;
-      a.dst_base = d.i_off * n + d.j_off;
-      a.dst_line = n;
-    }
-  } else {
-    a.n_lines = d.nj_loc;
-    a.n_walk = d.ni_loc;
-    a.line_rows = 1;
-    a.walk_rows = d.nj_loc;
-    a.dst_base = d.j_off * n + d.i_off;
-    a.dst_line = n;
-  }
+  if (geom->direction == TRIMUL_OUTGOING && geom->cp1 == 1 && static_cast<long>(d.ni_loc) * d.nj_loc > 0x7fffffffL)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token block too large");
+  trimul_reshard_plan_t plan;
+  derive_plan(geom, d, &plan);
+  a.batch_rows = plan.batch_rows;
+  a.n_lines = plan.n_lines;
+  a.n_walk = plan.n_walk;
+  a.line_rows = plan.line_rows;
+  a.walk_rows = plan.walk_rows;
+  a.dst_base = plan.dst_base;
+  a.dst_line = plan.dst_line;
   for (int s = 0; s < d.cp; ++s) {
     if (ab_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ab_peers[%d] is NULL", s);
     a.ab.ptr[s] = ab_peers[s];
   }
   a.d_loc_log2 = d.d_loc_log2;
-  a.plane_elems = n * n;
+  a.plane_elems = plan.plane_elems;
   a.gate_out = gate_out;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;

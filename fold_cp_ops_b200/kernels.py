@@ -60,6 +60,13 @@ def workspace_bytes(geom: _lib.Geom) -> _lib.Workspace:
     return ws
 
 
+def reshard_plan(geom: _lib.Geom) -> _lib.ReshardPlan:
+    """Host-side index arithmetic of the two fused reshards for this rank (no device work)."""
+    plan = _lib.ReshardPlan()
+    _lib.check(_lib.load().trimul_sm100_reshard_plan(C.byref(geom), C.byref(plan)), "trimul_sm100_reshard_plan")
+    return plan
+
+
 def new_status(device) -> torch.Tensor:
     """A zeroed device status record (8 x int32) for the bounded waits to report into."""
     return torch.zeros(8, dtype=torch.int32, device=device)

@@ -89,7 +89,33 @@ typedef struct trimul_workspace {
   uint64_t gate_bytes;
 } trimul_workspace_t;
 
+/* Index arithmetic of the two fused reshards for one rank (host-only; touches no device).
+ * Front: local token (b, line, w) is row  b*batch_rows + line*line_rows + w*walk_rows  of x and lands
+ * at element  ((h*d_loc + c)*batch + b)*plane_elems + dst_base + line*dst_line + w  of the `ab` buffer
+ * of the rank owning channel h*d + s*d_loc + c (h = 0 for a, 1 for b; s = owner).  Back: element
+ * (c, b, i, j) of this rank's contraction lands at  ((chan_offset + c)*batch + b)*ni_loc*nj_loc +
+ * (i % ni_loc)*nj_loc + (j % nj_loc)  of the `tri` buffer of rank (i / ni_loc)*cp1 + (j / nj_loc).
+ * Replaces the wire-layout description `ReshardLayout` (fold_cp_ops/distributed/reshard.py:63-377). */
+typedef struct trimul_reshard_plan {
+  int32_t n_lines;
+  int32_t n_walk;
+  int64_t batch_rows;
+  int64_t line_rows;
+  int64_t walk_rows;
+  int64_t plane_elems;
+  int64_t dst_base;
+  int64_t dst_line;
+  int32_t d_loc;
+  int32_t planes;
+  int32_t ni_loc;
+  int32_t nj_loc;
+  int32_t chan_offset;
+  int32_t pad;
+  int64_t rows;
+} trimul_reshard_plan_t;
+
 int trimul_sm100_query(int device, trimul_caps_t* out);
+int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* out);
 int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out);
 const char* trimul_sm100_last_error(void);
 
