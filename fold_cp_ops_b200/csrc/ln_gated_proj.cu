@@ -2,6 +2,9 @@
 //     xn   = LayerNorm(x) * gamma + beta                         (fp32 statistics, bf16 operand)
 //     a|b  = (xn Wp^T + bp) * sigmoid(xn Wg^T + bg) * mask       (2D channels, bf16)
 //     gate = sigmoid(xn Wo^T + bo)                               (D channels, bf16, stays local)
+// The packed weights and biases arrive pre-scaled by 1/2 (exact in bf16), so with p' = p/2 and
+// g' = g/2 the gated value is  p * sigmoid(g) = p' * tanh(g') + p'  -- one MUFU op and one FMA --
+// and the output gate is  0.5 * tanh(go') + 0.5.
 // (Reference: ops 1-5 and 10 of trimul_ref, fold_cp_ops/workflows/trimul_autotune.py:1505-1524;
 //  front kernel fold_cp_ops/distributed/dual_gated_gemm_a2a.py:56-76; K1 kernels/layernorm.py:730.)
 //
@@ -55,11 +58,51 @@ constexpr int smem_bytes() {
   return Cfg<D>::kTileBytes + 1024 + 256;
 }
 
-__device__ __forceinline__ float sigmoid_tanh(float x) {
-  // sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5 : one MUFU op instead of two
+__device__ __forceinline__ float tanh_approx(float x) {
   float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
-  return fmaf(0.5f, t, 0.5f);
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+
+// One 32-channel group of a gated chunk for this thread's token: pv = p/2, gv = g/2 accumulators.
+// Channels [0,16) go through base0, [16,32) through base1 (two owners when D/cp = 16).
+template <bool HAS_BIAS, bool HAS_MASK>
+__device__ __forceinline__ void store_gated_group(const uint32_t (&pv)[32], const uint32_t (&gv)[32],
+                                                  const float* bias_p, const float* bias_g, float mval,
+                                                  __nv_bfloat16* base0, __nv_bfloat16* base1, long chan_stride) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    float pr = __uint_as_float(pv[e]);
+    float ga = __uint_as_float(gv[e]);
+    if (HAS_BIAS) {
+      pr += __ldg(bias_p + e);
+      ga += __ldg(bias_g + e);
+    }
+    float val = fmaf(pr, tanh_approx(ga), pr);
+    if (HAS_MASK) val *= mval;
+    __nv_bfloat16* dst = (e < 16) ? base0 : base1;
+    dst[(e & 15) * chan_stride] = __float2bfloat16_rn(val);
+  }
+}
+
+template <bool HAS_BIAS>
+__device__ __forceinline__ void store_gate_group(const uint32_t (&gv)[32], const float* bias_g, uint4* dst) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float ga = __uint_as_float(gv[q * 8 + e]);
+      if (HAS_BIAS) ga += __ldg(bias_g + q * 8 + e);
+      s[e] = fmaf(0.5f, tanh_approx(ga), 0.5f);
+    }
+    uint4 pk;
+    pk.x = sm100::pack_bf16x2(s[0], s[1]);
+    pk.y = sm100::pack_bf16x2(s[2], s[3]);
+    pk.z = sm100::pack_bf16x2(s[4], s[5]);
+    pk.w = sm100::pack_bf16x2(s[6], s[7]);
+    dst[q] = pk;
+  }
 }
 
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
@@ -237,7 +280,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         for (int ps = 0; ps < PASSES; ++ps) {
           const int r = lw * ROWS_PER_WARP + half * BATCH_ROWS + ps * RPP + sub;
           const int w = tc.w0 + r;
-          if (w < p.n_walk) {
+          if (w < p.n_walk && !(p.debug_skip & 4)) {
             raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
           } else {
             raw[ps] = make_uint4(0, 0, 0, 0);
@@ -289,6 +332,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     const int r = quarter * 32 + lane;
     const int d_loc_mask = (1 << p.d_loc_log2) - 1;
     const int d_loc_n = 1 << p.d_loc_log2;
+    const long chan_stride = static_cast<long>(p.batch) * p.plane_elems;  // elements between channel planes
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -327,20 +371,23 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
             sm100::tmem_ld_32x32b_x32(trow + col0, pv);
             sm100::tmem_ld_32x32b_x32(trow + C::CH + col0, gv);
             sm100::tmem_ld_wait();
-            if (valid) {
+            if (valid && !(p.debug_skip & 1)) {
               const float* bias_p = p.bias + c * D + col0;
               const float* bias_g = bias_p + C::CH;
-              const int d0 = (c & 1) * C::CH + col0;  // channel inside the a (or b) half
+              const int d0 = (c & 1) * C::CH + col0;  // first channel of the group inside the a (or b) half
+              __nv_bfloat16* base[2];
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const float pr = __uint_as_float(pv[e]) + __ldg(bias_p + e);
-                const float ga = __uint_as_float(gv[e]) + __ldg(bias_g + e);
-                const float val = pr * sigmoid_tanh(ga) * mval;
-                const int d = d0 + e;
-                const int owner = d >> p.d_loc_log2;
+              for (int k = 0; k < 2; ++k) {
+                const int d = d0 + 16 * k;
                 const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
-                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[owner]);
-                dst[plane * p.plane_elems + dst_tok] = __float2bfloat16_rn(val);
+                base[k] = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
+              }
+              if (p.has_bias) {
+                if (p.mask_kind != 0) store_gated_group<true, true>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
+                else store_gated_group<true, false>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
+              } else {
+                if (p.mask_kind != 0) store_gated_group<false, true>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
+                else store_gated_group<false, false>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
               }
             }
           }
@@ -353,21 +400,11 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
             uint32_t gv[32];
             sm100::tmem_ld_32x32b_x32(trow + col0, gv);
             sm100::tmem_ld_wait();
-            if (valid) {
+            if (valid && !(p.debug_skip & 2)) {
               const float* bias_g = p.bias + 4 * D + col0;
               uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gate_out) + srow * D + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float s[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s[e] = sigmoid_tanh(__uint_as_float(gv[q * 8 + e]) + __ldg(bias_g + q * 8 + e));
-                uint4 pk;
-                pk.x = sm100::pack_bf16x2(s[0], s[1]);
-                pk.y = sm100::pack_bf16x2(s[2], s[3]);
-                pk.z = sm100::pack_bf16x2(s[4], s[5]);
-                pk.w = sm100::pack_bf16x2(s[6], s[7]);
-                dst[q] = pk;
-              }
+              if (p.has_bias) store_gate_group<true>(gv, bias_g, dst);
+              else store_gate_group<false>(gv, bias_g, dst);
             }
           }
         }

@@ -6,12 +6,14 @@
 // fold_cp_ops/workflows/trimul_autotune.py:1519-1525; fused consumer
 // fold_cp_ops/kernels/layernorm_dual_gated_gemm.py:5342; recv layout reshard.py:347-363.)
 //
-// Persistent CTA, 128-token tiles.  Eight LayerNorm warps read the tile channel-by-channel with
-// coalesced 128-byte warp loads (two tokens per lane), keep it in registers, combine per-token
-// statistics across the four channel groups with Chan's formula, and write the normalised bf16
-// operand into shared memory in the K-major 128-byte-swizzle layout.  W_out stays resident in
-// shared memory for the life of the CTA (one TMA load).  One thread issues tcgen05.mma, four
-// epilogue warps apply bias and gate and store 16-byte vectors token-major.
+// Persistent CTA, 128-token tiles.  Eight LayerNorm warps -- one per group of D/8 channels -- read
+// the tile in two 64-token halves with coalesced 128-byte warp loads (two tokens per lane) into
+// registers, double-buffered so the loads of the next half are in flight while the current one is
+// reduced; per-token statistics of the eight channel groups are combined with Chan's formula
+// through shared memory, and the normalised bf16 operand is written in the K-major
+// 128-byte-swizzle layout.  W_out stays resident in shared memory for the life of the CTA (one TMA
+// load).  One thread issues tcgen05.mma; eight epilogue warps prefetch their slice of the gate
+// before the accumulator is ready, then apply bias and gate and store 16-byte vectors token-major.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -20,13 +22,21 @@ namespace trimul {
 namespace {
 
 constexpr int BM = 128;
-constexpr int kThreads = 512;  // w0 TMA, w1 MMA, w2 TMEM alloc, w3 idle, w4-7 epilogue, w8-15 LayerNorm
+constexpr int HALF = 64;
+// Five warpgroups: w0-3 control (w0: TMEM alloc, W load, MMA issue), w4-11 epilogue, w12-19 LayerNorm.
+// The kernel launches at 96 registers per thread and rebalances with setmaxnreg: the control
+// warpgroup shrinks to 40, the epilogue grows to 104 and the LayerNorm warps to 112
+// (per SM sub-partition: (40 + 2*104 + 2*112) * 32 = 15104 <= 16384 registers).
+constexpr int kThreads = 640;
 constexpr int kEpiWarp0 = 4;
-constexpr int kLnWarp0 = 8;
+constexpr int kLnWarp0 = 12;
+constexpr int kCtlWarp = 0;
+constexpr int kGroups = 8;  // channel groups = LayerNorm warps
 
 template <int D>
 struct Cfg {
   static constexpr int KB = D / 64;
+  static constexpr int CPT = D / kGroups;  // channels per LayerNorm thread
   static constexpr int kABytes = BM * D * 2;
   static constexpr int kKBlockBytes = BM * 128;
   static constexpr int kWBytes = D * D * 2;
@@ -46,7 +56,7 @@ struct SmemCtl {
   uint64_t red_bar[2];  // LayerNorm warps: partial statistics of parity p are all written
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
-  float2 red[2][4][BM];  // [parity][channel group][token] = (mean, M2) partials
+  float2 red[2][kGroups][HALF];  // [parity][channel group][token of the half] = (mean, M2) partials
   float gamma[D];
   float beta[D];
 };
@@ -84,15 +94,17 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long total_tiles = (p.rows + BM - 1) / BM;
+  // tiles this CTA owns: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const long my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
     sm100::mbar_init(&ctl->w_full, 1);
     for (int a = 0; a < 2; ++a) {
-      sm100::mbar_init(&ctl->a_ready[a], 8);
+      sm100::mbar_init(&ctl->a_ready[a], kGroups);
       sm100::mbar_init(&ctl->a_empty[a], 1);
       sm100::mbar_init(&ctl->tmem_full[a], 1);
-      sm100::mbar_init(&ctl->tmem_empty[a], 4);
-      sm100::mbar_init(&ctl->red_bar[a], 8);
+      sm100::mbar_init(&ctl->tmem_empty[a], 8);
+      sm100::mbar_init(&ctl->red_bar[a], kGroups);
     }
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
@@ -101,7 +113,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
     ctl->gamma[i] = p.ln_w[i];
     ctl->beta[i] = p.ln_b ? p.ln_b[i] : 0.0f;
   }
-  if (warp == 2) {
+  if (warp == kCtlWarp) {
     sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
     sm100::tmem_relinquish();
   }
@@ -113,25 +125,23 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
   const uint64_t tmo = p.timeout_ns;
   bool w_armed = false;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ W_out: one TMA load, resident
-    if (lane == 0 && static_cast<long>(blockIdx.x) < total_tiles) {
+  if (warp < kEpiWarp0) {
+    sm100::setmaxnreg_dec<40>();
+    if (warp == kCtlWarp && lane == 0 && my_tiles > 0) {
+      // ---------------------------------------------------------- W_out: one TMA load, resident
       sm100::tma_prefetch_desc(&tmW);
       sm100::mbar_arrive_expect_tx(&ctl->w_full, C::kWBytes);
       for (int kb = 0; kb < C::KB; ++kb) {
         sm100::tma_load_2d(w_tiles + kb * C::kWBlockBytes, &tmW, &ctl->w_full, kb * 64, 0);
       }
       w_armed = true;
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0 && static_cast<long>(blockIdx.x) < total_tiles) {
+      // ---------------------------------------------------------- UMMA issuer
       constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
       bool ok = sm100::mbar_wait(&ctl->w_full, 0, abort_flag, tmo);
       if (!ok) report_timeout(p.status, kKernelOutProj, 1, -3);
       const uint32_t w_addr = sm100::smem_u32(w_tiles);
-      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (long it = 0; it < my_tiles && ok; ++it) {
         if (!sm100::mbar_wait(&ctl->a_ready[buf], buf_phase, abort_flag, tmo)) {
           report_timeout(p.status, kKernelOutProj, 1, -1);
           break;
@@ -166,26 +176,34 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
     }
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
-    constexpr int CPT = D / 4;                       // channels per thread
-    const int lt = threadIdx.x - kLnWarp0 * 32;      // 0..255
-    const int pr = lt & 63;                          // token pair: tokens 2*pr, 2*pr+1
-    const int cg = lt >> 6;                          // channel group
-    const int r0 = 2 * pr;
+    sm100::setmaxnreg_inc<112>();
+    constexpr int CPT = C::CPT;
+    const int cg = warp - kLnWarp0;  // channel group of this warp
+    const int r_in_half = 2 * lane;  // tokens 2*lane, 2*lane+1 of the half
     const uint8_t* tb = static_cast<const uint8_t*>(p.tri);
     uint32_t buf = 0, buf_phase = 0, par = 0, red_phase = 0;
-    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const long m0 = t * BM + r0;
-      const bool valid = m0 < p.rows;  // rows is even, so the pair is valid or invalid together
-      uint32_t v[CPT];
-      if (valid) {
+    bool ok = true;
+    const long total_halves = 2 * my_tiles;
+
+    auto load_half = [&](uint32_t (&v)[CPT], long h) {
+      const long t = blockIdx.x + (h >> 1) * gridDim.x;
+      const long m0 = t * BM + (h & 1) * HALF + r_in_half;
+      if (m0 < p.rows && !(p.debug_skip & 1)) {  // rows is even: the pair is valid or invalid together
+        const uint8_t* q = tb + (static_cast<long>(cg * CPT) * p.rows + m0) * 2;
+        const long plane_bytes = p.rows * 2;
 #pragma unroll
         for (int e = 0; e < CPT; ++e) {
-          v[e] = ldg_nc_u32(tb + (static_cast<long>(cg * CPT + e) * p.rows + m0) * 2);
+          v[e] = ldg_nc_u32(q);
+          q += plane_bytes;
         }
       } else {
 #pragma unroll
         for (int e = 0; e < CPT; ++e) v[e] = 0;
       }
+    };
+
+    auto process_half = [&](uint32_t (&v)[CPT], long h) {
+      const int half = static_cast<int>(h & 1);
       // local statistics over this thread's CPT channels, per token
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -202,46 +220,52 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
         q0 = fmaf(d0, d0, q0);
         q1 = fmaf(d1, d1, q1);
       }
-      ctl->red[par][cg][r0] = make_float2(lm0, q0);
-      ctl->red[par][cg][r0 + 1] = make_float2(lm1, q1);
+      *reinterpret_cast<float4*>(&ctl->red[par][cg][r_in_half]) = make_float4(lm0, q0, lm1, q1);
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->red_bar[par]);
-      bool ok = sm100::mbar_wait(&ctl->red_bar[par], (red_phase >> par) & 1, abort_flag, tmo);
+      ok = sm100::mbar_wait(&ctl->red_bar[par], (red_phase >> par) & 1, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        report_timeout(p.status, kKernelOutProj, 4, static_cast<int>(t));
-        break;
+        report_timeout(p.status, kKernelOutProj, 4, static_cast<int>(h));
+        return;
       }
       red_phase ^= (1u << par);
+      // combine the eight (mean, M2) partials; the partials are re-read for the second pass
+      // instead of being kept live, which saves 32 registers against the two in-flight halves
+      const float4* part = reinterpret_cast<const float4*>(&ctl->red[par][0][r_in_half]);
+      constexpr int kPartStride = HALF / 2;  // float4 elements between channel groups
       float mean0 = 0.f, mean1 = 0.f;
-      float2 pa[4], pb[4];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        pa[g] = ctl->red[par][g][r0];
-        pb[g] = ctl->red[par][g][r0 + 1];
-        mean0 += pa[g].x;
-        mean1 += pb[g].x;
+      for (int g = 0; g < kGroups; ++g) {
+        const float4 pg = part[g * kPartStride];
+        mean0 += pg.x;
+        mean1 += pg.z;
       }
-      mean0 *= 0.25f;
-      mean1 *= 0.25f;
+      mean0 *= (1.0f / kGroups);
+      mean1 *= (1.0f / kGroups);
       float m20 = 0.f, m21 = 0.f;
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const float e0 = pa[g].x - mean0, e1 = pb[g].x - mean1;
-        m20 += pa[g].y + CPT * e0 * e0;
-        m21 += pb[g].y + CPT * e1 * e1;
+      for (int g = 0; g < kGroups; ++g) {
+        const float4 pg = part[g * kPartStride];
+        const float e0 = pg.x - mean0, e1 = pg.z - mean1;
+        m20 += pg.y + CPT * e0 * e0;
+        m21 += pg.w + CPT * e1 * e1;
       }
       const float rstd0 = rsqrtf(m20 * (1.0f / D) + p.eps);
       const float rstd1 = rsqrtf(m21 * (1.0f / D) + p.eps);
-      par ^= 1;  // the next tile uses the other partial buffer: no second barrier needed
+      const float nm0 = -mean0 * rstd0, nm1 = -mean1 * rstd1;
+      par ^= 1;  // the next half uses the other partial buffer: no second barrier needed
 
-      ok = sm100::mbar_wait(&ctl->a_empty[buf], buf_phase ^ 1, abort_flag, tmo);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        report_timeout(p.status, kKernelOutProj, 3, static_cast<int>(t));
-        break;
+      if (half == 0) {
+        ok = sm100::mbar_wait(&ctl->a_empty[buf], buf_phase ^ 1, abort_flag, tmo);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          report_timeout(p.status, kKernelOutProj, 3, static_cast<int>(h));
+          return;
+        }
       }
       uint8_t* a_tile = a_tiles + buf * C::kABytes;
+      const int r0 = half * HALF + r_in_half;
 #pragma unroll
       for (int c8 = 0; c8 < CPT / 8; ++c8) {
         uint32_t lo[4], hi[4];
@@ -249,14 +273,14 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
         for (int e2 = 0; e2 < 4; ++e2) {
           const int e = c8 * 8 + e2 * 2;
           const int d = cg * CPT + e;
-          const float g0 = ctl->gamma[d], g1 = ctl->gamma[d + 1];
-          const float b0 = ctl->beta[d], b1 = ctl->beta[d + 1];
-          const float x00 = (sm100::bf16_lo(v[e]) - mean0) * rstd0;
-          const float x01 = (sm100::bf16_lo(v[e + 1]) - mean0) * rstd0;
-          const float x10 = (sm100::bf16_hi(v[e]) - mean1) * rstd1;
-          const float x11 = (sm100::bf16_hi(v[e + 1]) - mean1) * rstd1;
-          lo[e2] = sm100::pack_bf16x2(fmaf(x00, g0, b0), fmaf(x01, g1, b1));
-          hi[e2] = sm100::pack_bf16x2(fmaf(x10, g0, b0), fmaf(x11, g1, b1));
+          const float2 gm = *reinterpret_cast<const float2*>(&ctl->gamma[d]);
+          const float2 bt = *reinterpret_cast<const float2*>(&ctl->beta[d]);
+          const float x00 = fmaf(sm100::bf16_lo(v[e]), rstd0, nm0);
+          const float x01 = fmaf(sm100::bf16_lo(v[e + 1]), rstd0, nm0);
+          const float x10 = fmaf(sm100::bf16_hi(v[e]), rstd1, nm1);
+          const float x11 = fmaf(sm100::bf16_hi(v[e + 1]), rstd1, nm1);
+          lo[e2] = sm100::pack_bf16x2(fmaf(x00, gm.x, bt.x), fmaf(x01, gm.y, bt.y));
+          hi[e2] = sm100::pack_bf16x2(fmaf(x10, gm.x, bt.x), fmaf(x11, gm.y, bt.y));
         }
         const int chunk = (cg * CPT) / 8 + c8;  // 16-byte chunk index along K
         const uint32_t kb_off = (chunk >> 3) * C::kKBlockBytes;
@@ -265,22 +289,49 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
         *reinterpret_cast<uint4*>(a_tile + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         *reinterpret_cast<uint4*>(a_tile + o1) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       }
-      sm100::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&ctl->a_ready[buf]);
-      if (++buf == C::kABufs) {
-        buf = 0;
-        buf_phase ^= 1;
+      if (half == 1) {
+        sm100::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl->a_ready[buf]);
+        if (++buf == C::kABufs) {
+          buf = 0;
+          buf_phase ^= 1;
+        }
       }
+    };
+
+    uint32_t v0[CPT], v1[CPT];
+    if (total_halves > 0) load_half(v0, 0);
+    for (long h = 0; h < total_halves && ok; h += 2) {
+      load_half(v1, h + 1);  // total_halves is even: h + 1 always exists
+      process_half(v0, h);
+      if (!ok) break;
+      if (h + 2 < total_halves) load_half(v0, h + 2);
+      process_half(v1, h + 1);
     }
-  } else if (warp >= kEpiWarp0) {
-    // ------------------------------------------------------------ epilogue (4 warps)
+  } else {
+    // ------------------------------------------------------------ epilogue (8 warps)
+    sm100::setmaxnreg_inc<104>();
     const int quarter = warp & 3;
+    const int hh = (warp - kEpiWarp0) >> 2;  // which half of the output columns
     const int r = quarter * 32 + lane;
+    constexpr int COLS = D / 2;          // columns this warp handles
+    constexpr int NV = COLS / 8;         // 16-byte vectors of gate / out per thread
     uint32_t acc = 0, acc_phase = 0;
-    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (long it = 0; it < my_tiles; ++it) {
+      const long t = blockIdx.x + it * gridDim.x;
       const long m = t * BM + r;
       const bool valid = m < p.rows;
+      // the gate slice is fetched before the accumulator is ready: its latency hides behind the wait
+      uint4 gt[NV];
+      if (valid && !(p.debug_skip & 2)) {
+        const uint8_t* gp = static_cast<const uint8_t*>(p.gate) + (m * D + hh * COLS) * 2;
+#pragma unroll
+        for (int q = 0; q < NV; ++q) gt[q] = ldg_nc_v4(gp + q * 16);
+      } else {
+#pragma unroll
+        for (int q = 0; q < NV; ++q) gt[q] = make_uint4(0, 0, 0, 0);
+      }
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -288,36 +339,31 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
         break;
       }
       sm100::tcgen05_fence_after_sync();
-      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
-      constexpr int GROUPS = D / 32;
-#pragma unroll 1
-      for (int g = 0; g < GROUPS; ++g) {
-        const int col0 = g * 32;
-        uint32_t pv[32];
-        sm100::tmem_ld_32x32b_x32(trow + col0, pv);
-        uint4 gt[4];
-        if (valid) {
-          const uint8_t* gp = static_cast<const uint8_t*>(p.gate) + (m * D + col0) * 2;
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D + hh * COLS;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + m * D + hh * COLS);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) gt[q] = ldg_nc_v4(gp + q * 16);
-        }
+      for (int g = 0; g < COLS / 16; ++g) {
+        uint32_t pv[16];
+        sm100::tmem_ld_32x32b_x16(trow + g * 16, pv);
         sm100::tmem_ld_wait();
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + m * D + col0);
+        if (valid && !(p.debug_skip & 4)) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t gw[4] = {gt[q].x, gt[q].y, gt[q].z, gt[q].w};
+          for (int q = 0; q < 2; ++q) {
+            const uint4 gq = gt[g * 2 + q];
+            const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
             uint32_t ow[4];
 #pragma unroll
             for (int e2 = 0; e2 < 4; ++e2) {
               const int e = q * 8 + e2 * 2;
-              const float b0 = p.bias ? __ldg(p.bias + col0 + e) : 0.0f;
-              const float b1 = p.bias ? __ldg(p.bias + col0 + e + 1) : 0.0f;
-              const float y0 = (__uint_as_float(pv[e]) + b0) * sm100::bf16_lo(gw[e2]);
-              const float y1 = (__uint_as_float(pv[e + 1]) + b1) * sm100::bf16_hi(gw[e2]);
-              ow[e2] = sm100::pack_bf16x2(y0, y1);
+              float y0 = __uint_as_float(pv[e]);
+              float y1 = __uint_as_float(pv[e + 1]);
+              if (p.bias != nullptr) {
+                y0 += __ldg(p.bias + hh * COLS + g * 16 + e);
+                y1 += __ldg(p.bias + hh * COLS + g * 16 + e + 1);
+              }
+              ow[e2] = sm100::pack_bf16x2(y0 * sm100::bf16_lo(gw[e2]), y1 * sm100::bf16_hi(gw[e2]));
             }
-            dst[q] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            dst[g * 2 + q] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           }
         }
       }
@@ -334,14 +380,14 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const OutProjArgs p) {
   // ------------------------------------------------------------------ teardown
   __syncwarp();  // single-lane roles reconverge with their warp
   __syncthreads();
-  if (warp == 0 && lane == 0 && w_armed) {
+  if (warp == kCtlWarp && lane == 0 && w_armed) {
     // the weight load is the only TMA copy of this kernel; make sure it landed before exit
     const uint64_t t0 = sm100::globaltimer_ns();
     while (!sm100::mbar_test(&ctl->w_full, 0) && sm100::globaltimer_ns() - t0 < 2000000ull) {
     }
   }
   __syncthreads();
-  if (warp == 2) {
+  if (warp == kCtlWarp) {
     sm100::tcgen05_fence_after_sync();
     sm100::tmem_dealloc(tmem_base, C::kTmemCols);
   }

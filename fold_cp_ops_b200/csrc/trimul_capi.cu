@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/trimul_sm100.h"
@@ -74,6 +75,13 @@ int num_sms_current() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
   }
   return cached[dev];
+}
+
+// Profiling aid: TRIMUL_DEBUG_SKIP=<bits> makes a kernel leave out one of its memory streams so its
+// cost can be measured in isolation (results are then wrong by construction).  Unset in normal use.
+int debug_skip_bits() {
+  const char* e = getenv("TRIMUL_DEBUG_SKIP");
+  return e ? atoi(e) : 0;
 }
 
 struct Derived {
@@ -178,8 +186,11 @@ __global__ void pack_weights_kernel(int d, const __nv_bfloat16* p_in, const __nv
     src = g_out + static_cast<long>(rr) * d;
     bias = g_out_b ? g_out_b[rr] : 0.0f;
   }
-  for (int c = threadIdx.x; c < d; c += blockDim.x) w_packed[static_cast<long>(row) * d + c] = src[c];
-  if (threadIdx.x == 0) bias_packed[row] = bias;
+  // every packed row and bias carries a factor 1/2 (exact in bf16): the projection kernel turns
+  // p * sigmoid(g) into (p/2) * tanh(g/2) + p/2 and sigmoid(go) into 0.5 * tanh(go/2) + 0.5
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    w_packed[static_cast<long>(row) * d + c] = __float2bfloat16_rn(0.5f * __bfloat162float(src[c]));
+  if (threadIdx.x == 0) bias_packed[row] = 0.5f * bias;
 }
 
 }  // namespace
@@ -248,7 +259,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   Derived d;
   int rc = check_geom(geom, &d);
   if (rc != TRIMUL_OK) return rc;
-  if (!x || !ln_w || !w_packed || !bias_packed || !ab_peers || !gate_out)
+  if (!x || !ln_w || !w_packed || !ab_peers || !gate_out)
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: NULL pointer");
   if (mask_kind < 0 || mask_kind > 3 || (mask_kind != 0 && mask == nullptr))
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: bad mask_kind %d", mask_kind);
@@ -269,6 +280,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   a.ln_w = ln_w;
   a.ln_b = ln_b;
   a.bias = bias_packed;
+  a.has_bias = bias_packed != nullptr ? 1 : 0;
   a.eps = geom->eps;
   a.D = D;
   a.batch = geom->batch;
@@ -290,6 +302,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   a.d_loc_log2 = d.d_loc_log2;
   a.plane_elems = plan.plane_elems;
   a.gate_out = gate_out;
+  a.debug_skip = debug_skip_bits() & 7;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
   cudaError_t e = trimul::launch_gated_proj(tmW, a, num_sms_current(), stream);
@@ -365,6 +378,7 @@ int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, c
   a.eps = geom->eps;
   a.D = D;
   a.rows = d.rows;
+  a.debug_skip = (debug_skip_bits() >> 4) & 7;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
   cudaError_t e = trimul::launch_out_proj(tmW, a, num_sms_current(), stream);

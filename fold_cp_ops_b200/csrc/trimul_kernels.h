@@ -24,7 +24,8 @@ struct GatedProjArgs {
   int mask_kind;         // 0 none, 1 bf16, 2 fp32, 3 uint8/bool
   const float* ln_w;     // (D,)
   const float* ln_b;     // (D,) or nullptr
-  const float* bias;     // (5*D,) fp32 in PACKED row order (zeros where the layer has no bias)
+  const float* bias;     // (5*D,) fp32 in PACKED row order, pre-scaled by 1/2 (zeros where the layer has no bias)
+  int has_bias;          // 0: every packed bias is zero, the epilogue skips the loads
   float eps;
   int D;
   int batch;
@@ -39,6 +40,7 @@ struct GatedProjArgs {
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane
   void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
+  int debug_skip;        // profiling aid (TRIMUL_DEBUG_SKIP): bit0 skip a|b stores, bit1 skip gate stores, bit2 skip x loads
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
@@ -79,6 +81,7 @@ struct OutProjArgs {
   float eps;
   int D;
   long rows;
+  int debug_skip;        // profiling aid: bit0 skip tri loads, bit1 skip gate loads, bit2 skip out stores
   DeviceStatus* status;
   uint64_t timeout_ns;
 };

@@ -72,6 +72,8 @@ class PackedWeights:
         self.w_packed, self.bias_packed = K.pack_weights(
             D, b16(w["p_in_w"]), b16(w["g_in_w"]), b16(w["g_out_w"]), f32(w.get("p_in_b")), f32(w.get("g_in_b")),
             f32(w.get("g_out_b")))
+        if all(w.get(k) is None for k in ("p_in_b", "g_in_b", "g_out_b")):
+            self.bias_packed = None  # lets the projection kernel skip every bias load
 
 
 class TriMulEngine:

@@ -122,7 +122,8 @@ const char* trimul_sm100_last_error(void);
 /* Pack the input-side weights once at construction: rows of p_in / g_in / g_out (each row-major
  * (out, in), bf16) are regrouped into five d-row chunks [a_lo|a_hi|b_lo|b_hi: d/2 projection rows
  * then the d/2 matching gate rows][g_out: d rows]; biases (fp32, any may be NULL) are packed the
- * same way.  w_packed: (5d, d) bf16; bias_packed: (5d) fp32.
+ * same way.  Every packed row and bias is scaled by 1/2 (exact), which lets the kernel evaluate
+ * p * sigmoid(g) as (p/2) * tanh(g/2) + p/2.  w_packed: (5d, d) bf16; bias_packed: (5d) fp32.
  * Replaces `interleave_dual_weights` (fold_cp_ops/kernels/dual_gated_gemm.py:958). */
 int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
                               const float* p_in_b, const float* g_in_b, const float* g_out_b, void* w_packed,
@@ -131,7 +132,7 @@ int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w,
 /* Stage 1+2: input LayerNorm fused into the gated dual projection, front reshard fused in the
  * store.  x: this rank's (batch, n/cp0, n/cp1, d) block; mask: one scalar per local token or NULL;
  * ab_peers[s]: base of rank s's `ab` buffer (cp0*cp1 entries; entry `rank` is local memory);
- * gate_out: local `gate` buffer.
+ * gate_out: local `gate` buffer; bias_packed may be NULL when the layer has no projection bias.
  * Replaces `layernorm_fwd` (fold_cp_ops/kernels/layernorm.py:730) + `DualGatedGemmDistStore.run`
  * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:1744) + the g_out half of
  * `layernorm_dual_gated_gemm` (fold_cp_ops/kernels/layernorm_dual_gated_gemm.py:5342). */
