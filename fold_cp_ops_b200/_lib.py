@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "trimul_sm100_reshard_plan",
     "trimul_sm100_last_error",
     "trimul_sm100_pack_weights",
+    "trimul_sm100_pack_out_weights",
     "trimul_sm100_ln_gated_proj",
     "trimul_sm100_tri_contract",
     "trimul_sm100_ln_out_proj",
@@ -103,12 +104,14 @@ def load():
         lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p,
                                                    C.POINTER(vp), vp, vp, u64, vp]
         lib.trimul_sm100_tri_contract.argtypes = [C.POINTER(Geom), vp, C.POINTER(vp), vp, u64, vp]
-        lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, f32p, f32p, vp, f32p, vp, vp, u64, vp]
-        lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, f32p, f32p,
-                                             vp, f32p, vp, vp, vp, vp, vp, u64, vp]
+        lib.trimul_sm100_pack_out_weights.argtypes = [i32, vp, f32p, f32p, f32p, vp, f32p, vp]
+        lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, vp, f32p, vp, vp, u64, vp]
+        lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, vp, f32p,
+                                             vp, vp, vp, vp, vp, u64, vp]
         lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, vp]
         lib.trimul_sm100_peer_wait.argtypes = [vp, i32, u64, vp, u64, vp]
         for name in ("trimul_sm100_query", "trimul_sm100_workspace", "trimul_sm100_pack_weights",
+                     "trimul_sm100_pack_out_weights",
                      "trimul_sm100_ln_gated_proj", "trimul_sm100_tri_contract", "trimul_sm100_ln_out_proj",
                      "trimul_sm100_forward", "trimul_sm100_peer_signal", "trimul_sm100_peer_wait"):
             getattr(lib, name).restype = C.c_int

@@ -171,6 +171,20 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major bf16 operand (the M/N index is the contiguous
+// one) staged by TMA with the 128-byte swizzle along M/N: one 128-byte row holds 64 consecutive
+// M/N elements of one K index, eight K rows form a 1024-byte swizzle atom.  `lbo` is the byte
+// distance between successive 64-element M/N blocks, `sbo` between successive 8-row K groups.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32;
+  d |= static_cast<uint64_t>(1) << 46;             // version
+  d |= static_cast<uint64_t>(2) << 61;             // SWIZZLE_128B
+  return d;
+}
+
 // Instruction descriptor for kind::f16, bf16 x bf16 -> fp32, both operands K-major, dense.
 //   [4,6) D format (1 = f32)  [7,10) A format (1 = bf16)  [10,13) B format (1 = bf16)
 //   [15] A major  [16] B major (0 = K)  [17,23) N >> 3  [24,29) M >> 4

@@ -193,6 +193,42 @@ __global__ void pack_weights_kernel(int d, const __nv_bfloat16* p_in, const __nv
   if (threadIdx.x == 0) bias_packed[row] = 0.5f * bias;
 }
 
+
+// Fold the output LayerNorm into the output projection (runs once per layer).  One block per
+// output row n:  w_fold[n,k] = bf16(gamma_k * W[n,k]);  c[n] = sum_k w_fold[n,k];
+// d[n] = sum_k beta_k * W[n,k] + b[n].
+__global__ void pack_out_weights_kernel(int d, const __nv_bfloat16* w_out, const float* ln_w, const float* ln_b,
+                                        const float* bias, __nv_bfloat16* w_fold, float* cd) {
+  const int n = blockIdx.x;
+  float c = 0.f, dd = 0.f;
+  for (int k = threadIdx.x; k < d; k += blockDim.x) {
+    const float w = __bfloat162float(w_out[static_cast<long>(n) * d + k]);
+    const __nv_bfloat16 wf = __float2bfloat16_rn(ln_w[k] * w);
+    w_fold[static_cast<long>(n) * d + k] = wf;
+    c += __bfloat162float(wf);
+    dd += (ln_b ? ln_b[k] : 0.f) * w;
+  }
+  __shared__ float sc[32], sd[32];
+  for (int o = 16; o >= 1; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    dd += __shfl_xor_sync(0xffffffffu, dd, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sc[threadIdx.x >> 5] = c;
+    sd[threadIdx.x >> 5] = dd;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tc = 0.f, td = 0.f;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) {
+      tc += sc[w];
+      td += sd[w];
+    }
+    cd[2 * n] = tc;
+    cd[2 * n + 1] = td + (bias ? bias[n] : 0.f);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -249,6 +285,17 @@ int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w,
       bias_packed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pack_weights launch");
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_pack_out_weights(int32_t d, const void* w_out, const float* ln_w, const float* ln_b,
+                                  const float* bias_out, void* w_fold, float* cd, trimul_stream_t stream) {
+  if (d != 128 && d != 256) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
+  if (!w_out || !ln_w || !w_fold || !cd) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "pack_out_weights: NULL pointer");
+  pack_out_weights_kernel<<<d, 128, 0, stream>>>(d, static_cast<const __nv_bfloat16*>(w_out), ln_w, ln_b, bias_out,
+                                                 static_cast<__nv_bfloat16*>(w_fold), cd);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pack_out_weights launch");
   return TRIMUL_OK;
 }
 
@@ -350,47 +397,53 @@ int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, v
   return TRIMUL_OK;
 }
 
-int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate,
-                             const float* ln_w, const float* ln_b, const void* w_out, const float* bias_out,
-                             void* out, trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate, const void* w_fold,
+                             const float* cd, void* out, trimul_status_t* status, uint64_t timeout_ns,
+                             trimul_stream_t stream) {
   Derived d;
   int rc = check_geom(geom, &d);
   if (rc != TRIMUL_OK) return rc;
-  if (!tri_local || !gate || !ln_w || !w_out || !out)
+  if (!tri_local || !gate || !w_fold || !cd || !out)
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_out_proj: NULL pointer");
   const int D = geom->d;
-  CUtensorMap tmW;
+  CUtensorMap tmW, tmT;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(D)};
     const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
     const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
-    rc = make_tmap(&tmW, w_out, 2, dims, strides, box);
+    rc = make_tmap(&tmW, w_fold, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  {
+    // tri as (tokens contiguous, channels): the tile is consumed token-major exactly as stored
+    const uint64_t dims[2] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d.rows) * 2};
+    const uint32_t box[2] = {64, 64};
+    rc = make_tmap(&tmT, tri_local, 2, dims, strides, box);
     if (rc != TRIMUL_OK) return rc;
   }
   trimul::OutProjArgs a;
   memset(&a, 0, sizeof(a));
-  a.tri = tri_local;
   a.gate = gate;
-  a.ln_w = ln_w;
-  a.ln_b = ln_b;
-  a.bias = bias_out;
+  a.cd = cd;
   a.out = out;
   a.eps = geom->eps;
   a.D = D;
   a.rows = d.rows;
   a.debug_skip = (debug_skip_bits() >> 4) & 7;
+  a.mn_swap = (debug_skip_bits() >> 8) & 1;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_out_proj(tmW, a, num_sms_current(), stream);
+  cudaError_t e = trimul::launch_out_proj(tmW, tmT, a, num_sms_current(), stream);
   if (e != cudaSuccess) return cuda_fail(e, "ln_out_proj launch");
   return TRIMUL_OK;
 }
 
 int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
                          const float* ln_in_w, const float* ln_in_b, const void* w_packed,
-                         const float* bias_packed, const float* ln_out_w, const float* ln_out_b,
-                         const void* w_out, const float* bias_out, void* ab, void* tri, void* gate, void* out,
-                         trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+                         const float* bias_packed, const void* w_fold, const float* cd, void* ab, void* tri,
+                         void* gate, void* out, trimul_status_t* status, uint64_t timeout_ns,
+                         trimul_stream_t stream) {
   if (geom == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "geom is NULL");
   if (geom->cp0 != 1 || geom->cp1 != 1)
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "trimul_sm100_forward is the single-GPU chain; cp grid must be 1 x 1");
@@ -401,8 +454,7 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
   if (rc != TRIMUL_OK) return rc;
   rc = trimul_sm100_tri_contract(geom, ab, tri_peers, status, timeout_ns, stream);
   if (rc != TRIMUL_OK) return rc;
-  return trimul_sm100_ln_out_proj(geom, tri, gate, ln_out_w, ln_out_b, w_out, bias_out, out, status, timeout_ns,
-                                  stream);
+  return trimul_sm100_ln_out_proj(geom, tri, gate, w_fold, cd, out, status, timeout_ns, stream);
 }
 
 }  // extern "C"

@@ -53,7 +53,8 @@ class PackedWeights:
 
     LayerNorm gains / biases and projection biases stay fp32; the six projection matrices are
     bf16; the three input-side matrices are regrouped into the five chunk order of
-    ``trimul_sm100_pack_weights``."""
+    ``trimul_sm100_pack_weights`` (pre-scaled by 1/2); the output LayerNorm is folded into the output
+    projection by ``trimul_sm100_pack_out_weights``."""
 
     def __init__(self, w: Dict[str, Optional[torch.Tensor]], device: torch.device):
         D = int(w["norm_in_w"].shape[0])
@@ -66,9 +67,9 @@ class PackedWeights:
         f32 = lambda t: None if t is None else t.detach().to(device=device, dtype=torch.float32).contiguous()
         b16 = lambda t: t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
         self.norm_in_w, self.norm_in_b = f32(w["norm_in_w"]), f32(w.get("norm_in_b"))
-        self.norm_out_w, self.norm_out_b = f32(w["norm_out_w"]), f32(w.get("norm_out_b"))
-        self.p_out_w = b16(w["p_out_w"])
-        self.p_out_b = f32(w.get("p_out_b"))
+        # the output LayerNorm is folded into the output projection: bf16(gamma * W) and (c, d) constants
+        self.w_fold, self.cd = K.pack_out_weights(D, b16(w["p_out_w"]), f32(w["norm_out_w"]), f32(w.get("norm_out_b")),
+                                                  f32(w.get("p_out_b")))
         self.w_packed, self.bias_packed = K.pack_weights(
             D, b16(w["p_in_w"]), b16(w["g_in_w"]), b16(w["g_out_w"]), f32(w.get("p_in_b")), f32(w.get("g_in_b")),
             f32(w.get("g_out_b")))
@@ -239,8 +240,7 @@ class _Workspace:
                 self.flags.back_done()
             if log:
                 ev[2].record()
-            K.ln_out_proj(geom, self.tri, self.gate, W.norm_out_w, W.norm_out_b, W.p_out_w, W.p_out_b, os_,
-                          eng.status, eng.timeout_ns)
+            K.ln_out_proj(geom, self.tri, self.gate, W.w_fold, W.cd, os_, eng.status, eng.timeout_ns)
             if self.flags is not None:
                 self.flags.consumed()
             if log:

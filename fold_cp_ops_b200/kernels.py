@@ -149,29 +149,46 @@ def tri_contract(geom, ab_local, tri_peer_ptrs: Sequence[int], status, timeout_n
     _lib.check(rc, "trimul_sm100_tri_contract")
 
 
-def ln_out_proj(geom, tri_local, gate, ln_w, ln_b, w_out, bias_out, out, status,
-                timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+def pack_out_weights(d: int, p_out_w, ln_w, ln_b=None, p_out_b=None):
+    """Fold the output LayerNorm into the output projection.
+
+    Returns ``(w_fold (d, d) bf16 = bf16(ln_w * W), cd (d, 2) fp32 = (sum_k w_fold, sum_k ln_b*W + bias))``.
+    """
+    _require(p_out_w, torch.bfloat16, "p_out_w")
+    _require(ln_w, torch.float32, "ln_w")
+    if tuple(p_out_w.shape) != (d, d):
+        raise ValueError(f"p_out_w must have shape {(d, d)}; got {tuple(p_out_w.shape)}")
+    for t, nm in ((ln_b, "ln_b"), (p_out_b, "p_out_b")):
+        if t is not None:
+            _require(t, torch.float32, nm)
+    w_fold = torch.empty(d, d, dtype=torch.bfloat16, device=p_out_w.device)
+    cd = torch.empty(d, 2, dtype=torch.float32, device=p_out_w.device)
+    rc = _lib.load().trimul_sm100_pack_out_weights(d, _ptr(p_out_w), _ptr(ln_w), _ptr(ln_b), _ptr(p_out_b),
+                                                   _ptr(w_fold), _ptr(cd), _stream())
+    _lib.check(rc, "trimul_sm100_pack_out_weights")
+    return w_fold, cd
+
+
+def ln_out_proj(geom, tri_local, gate, w_fold, cd, out, status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
     _require(tri_local, torch.bfloat16, "tri_local")
     _require(gate, torch.bfloat16, "gate")
-    _require(ln_w, torch.float32, "ln_w")
-    _require(w_out, torch.bfloat16, "w_out")
+    _require(w_fold, torch.bfloat16, "w_fold")
+    _require(cd, torch.float32, "cd")
     _require(out, torch.bfloat16, "out")
-    rc = _lib.load().trimul_sm100_ln_out_proj(C.byref(geom), _ptr(tri_local), _ptr(gate), _ptr(ln_w), _ptr(ln_b),
-                                              _ptr(w_out), _ptr(bias_out), _ptr(out), _ptr(status),
-                                              int(timeout_ns), _stream())
+    rc = _lib.load().trimul_sm100_ln_out_proj(C.byref(geom), _ptr(tri_local), _ptr(gate), _ptr(w_fold), _ptr(cd),
+                                              _ptr(out), _ptr(status), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_ln_out_proj")
 
 
-def forward_single(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, ln_out_w, ln_out_b, w_out, bias_out,
-                   ab, tri, gate, out, status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+def forward_single(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, w_fold, cd, ab, tri, gate, out, status,
+                   timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
     """The whole cp=1 chain through ``trimul_sm100_forward``."""
     _require(x, torch.bfloat16, "x")
     _require(out, torch.bfloat16, "out")
     mptr, mkind = _mask_args(mask)
     rc = _lib.load().trimul_sm100_forward(C.byref(geom), _ptr(x), mptr, mkind, _ptr(ln_in_w), _ptr(ln_in_b),
-                                          _ptr(w_packed), _ptr(bias_packed), _ptr(ln_out_w), _ptr(ln_out_b),
-                                          _ptr(w_out), _ptr(bias_out), _ptr(ab), _ptr(tri), _ptr(gate), _ptr(out),
-                                          _ptr(status), int(timeout_ns), _stream())
+                                          _ptr(w_packed), _ptr(bias_packed), _ptr(w_fold), _ptr(cd), _ptr(ab),
+                                          _ptr(tri), _ptr(gate), _ptr(out), _ptr(status), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_forward")
 
 

@@ -148,19 +148,28 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
 int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, void* const* tri_peers,
                               trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
 
+/* Fold the output LayerNorm into the output projection once at construction:
+ *   w_fold[n,k] = bf16(ln_w[k] * w_out[n,k])            (d, d) bf16
+ *   cd[n] = { sum_k w_fold[n,k],  sum_k ln_b[k] * w_out[n,k] + bias_out[n] }   (d, 2) fp32
+ * so that LN(x) w_out^T + b = rstd * (x w_fold^T - mean * c) + d.  ln_b and bias_out may be NULL.
+ * Replaces `_fold_precompute_kernel` (fold_cp_ops/kernels/layernorm_dual_gated_gemm.py:4617). */
+int trimul_sm100_pack_out_weights(int32_t d, const void* w_out, const float* ln_w, const float* ln_b,
+                                  const float* bias_out, void* w_fold, float* cd, trimul_stream_t stream);
+
 /* Stage 4: output LayerNorm fused with the output projection, gated.  out: (batch, n/cp0, n/cp1, d).
+ * w_fold / cd come from trimul_sm100_pack_out_weights.
  * Replaces `_consume` (fold_cp_ops/distributed/workflows/trimul_autotuned.py:3482-3550). */
-int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate,
-                             const float* ln_w, const float* ln_b, const void* w_out, const float* bias_out,
-                             void* out, trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate, const void* w_fold,
+                             const float* cd, void* out, trimul_status_t* status, uint64_t timeout_ns,
+                             trimul_stream_t stream);
 
 /* The whole single-GPU forward (cp0 = cp1 = 1): stages 1-4 back to back on `stream`.
  * Replaces `trimul_autotuned` (fold_cp_ops/workflows/trimul_autotune.py:1531). */
 int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
                          const float* ln_in_w, const float* ln_in_b, const void* w_packed,
-                         const float* bias_packed, const float* ln_out_w, const float* ln_out_b,
-                         const void* w_out, const float* bias_out, void* ab, void* tri, void* gate, void* out,
-                         trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+                         const float* bias_packed, const void* w_fold, const float* cd, void* ab, void* tri,
+                         void* gate, void* out, trimul_status_t* status, uint64_t timeout_ns,
+                         trimul_stream_t stream);
 
 /* Rank-to-rank ordering of the fused reshards.  Every rank owns a symmetric array of 16 uint64
  * counters (zeroed once).  `peer_signal` adds 1 to counter `slot` on every rank listed in

@@ -213,13 +213,16 @@ def test_kernel_tri_contract(N, planes_d):
     assert (err <= 2.0 ** -8 * want.abs() + 1e-3 * want.abs().max()).all(), err.max().item()
 
 
-@pytest.mark.parametrize("D,B,n", [(128, 1, 8), (128, 1, 72), (256, 2, 40)])
-def test_kernel_ln_out_proj(D, B, n):
+@pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0)])
+def test_kernel_ln_out_proj(D, B, n, offset):
+    """The folded LayerNorm (rstd * (x W'^T - mean c) + d) against an explicit fp32 LayerNorm; the last
+    case shifts every token's channels far off zero (|mean| = 10 sigma), where the fold subtracts two
+    large numbers."""
     from fold_cp_ops_b200 import kernels as K
 
     rows = B * n * n
     torch.manual_seed(rows)
-    tri = (3.0 * torch.randn(D, rows, device=DEV) + 0.5).to(torch.bfloat16)
+    tri = (3.0 * torch.randn(D, rows, device=DEV) + offset).to(torch.bfloat16)
     gate = torch.rand(rows, D, device=DEV).to(torch.bfloat16)
     lw = (1 + 0.1 * torch.randn(D, device=DEV)).float()
     lb = (0.1 * torch.randn(D, device=DEV)).float()
@@ -227,14 +230,16 @@ def test_kernel_ln_out_proj(D, B, n):
     bo = (0.02 * torch.randn(D, device=DEV)).float()
     out = torch.full((rows, D), float("nan"), dtype=torch.bfloat16, device=DEV)
     st = K.new_status(DEV)
-    K.ln_out_proj(K.make_geom(B, n, D, "outgoing", 1e-5), tri, gate, lw, lb, w, bo, out, st)
+    w_fold, cd = K.pack_out_weights(D, w, lw, lb, bo)
+    K.ln_out_proj(K.make_geom(B, n, D, "outgoing", 1e-5), tri, gate, w_fold, cd, out, st)
     torch.cuda.synchronize()
     K.check_status(st)
     torch.backends.cuda.matmul.allow_tf32 = False
-    trin = layer_norm(tri.float().t(), lw, lb, 1e-5).to(torch.bfloat16).float()
+    trin = layer_norm(tri.float().t(), lw, lb, 1e-5)
     want = (trin @ w.float().t() + bo) * gate.float()
     err = (out.float() - want).abs()
-    assert (err <= 0.03 + 0.02 * want.abs()).all(), err.max().item()
+    tol = 0.03 + 0.02 * want.abs() if offset < 1 else 0.08 + 0.03 * want.abs()
+    assert (err <= tol).all(), err.max().item()
 
 
 # ------------------------------------------------------------------------------------------------
