@@ -9,12 +9,13 @@
 //  front kernel fold_cp_ops/distributed/dual_gated_gemm_a2a.py:56-76; K1 kernels/layernorm.py:730.)
 //
 // Persistent CTA, 128-token tiles.  Eight LayerNorm warps pull token rows from HBM into
-// registers, normalise, and write the bf16 operand tile into shared memory in the K-major
-// 128-byte-swizzle layout the tensor core reads; weights stream through a TMA ring (they live in
-// L2); one thread issues tcgen05.mma for five N=D column chunks per tile into two TMEM
-// accumulators; eight epilogue warps apply bias / sigmoid gate / mask and store each channel's
-// 128 tokens contiguously into the channel-major operand plane of the rank that owns the channel
-// (front all-to-all fused in the store; at cp=1 that rank is this GPU).
+// registers, normalise them there (two-pass fp32 statistics), and write the bf16 operand tile into
+// shared memory in the K-major 128-byte-swizzle layout once the tensor core has released it;
+// weights stream through a four-stage TMA ring (they live in L2); one thread issues tcgen05.mma
+// for five N=D column chunks per tile into two TMEM accumulators; eight epilogue warps apply bias /
+// gate / mask, transpose 32-channel x 32-token blocks through a small per-warp shared-memory
+// stage, and store 16-byte vectors into the channel-major operand plane of the rank that owns
+// the channel (front all-to-all fused in the store; at cp=1 that rank is this GPU).
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -23,10 +24,15 @@ namespace trimul {
 namespace {
 
 constexpr int BM = 128;
-constexpr int kThreads = 640;       // w0 TMA, w1 MMA, w2 TMEM alloc, w3 idle, w4-11 epilogue, w12-19 LayerNorm
+// Five warpgroups: w0-3 control (w0 weight TMA, w1 MMA issue, w2 TMEM alloc), w4-11 epilogue,
+// w12-19 LayerNorm.  Launched at 96 registers per thread and rebalanced with setmaxnreg:
+// control 40, epilogue 104, LayerNorm 112 ((40 + 2*104 + 2*112) * 32 = 15104 <= 16384 per SMSP).
+constexpr int kThreads = 640;
 constexpr int kEpiWarp0 = 4;
 constexpr int kLnWarp0 = 12;
-constexpr int kNumChunks = 5;       // a_lo, a_hi, b_lo, b_hi, gate
+constexpr int kNumChunks = 5;            // a_lo, a_hi, b_lo, b_hi, gate
+constexpr int kStagePitch = 80;          // bytes per channel row of the transpose stage (64 + 16 pad)
+constexpr int kStageBytes = 32 * kStagePitch;
 
 template <int D>
 struct Cfg {
@@ -35,9 +41,10 @@ struct Cfg {
   static constexpr int kABytes = BM * D * 2;    // one operand tile
   static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
   static constexpr int kWStageBytes = D * 128;  // D weight rows x 64 k
-  static constexpr int kWStages = (D == 256) ? 3 : 4;
+  static constexpr int kWStages = 4;
+  static constexpr int kABufs = (D == 256) ? 1 : 2;
   static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
-  static constexpr int kTileBytes = 2 * kABytes + kWStages * kWStageBytes;
+  static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes;
 };
 
 template <int D>
@@ -51,11 +58,12 @@ struct SmemCtl {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kWStages];
+  alignas(16) uint8_t stage[8][kStageBytes];  // one transpose stage per epilogue warp
 };
 
 template <int D>
 constexpr int smem_bytes() {
-  return Cfg<D>::kTileBytes + 1024 + 256;
+  return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
 __device__ __forceinline__ float tanh_approx(float x) {
@@ -64,12 +72,11 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return t;
 }
 
-// One 32-channel group of a gated chunk for this thread's token: pv = p/2, gv = g/2 accumulators.
-// Channels [0,16) go through base0, [16,32) through base1 (two owners when D/cp = 16).
+// One 32-channel group of a gated chunk: this thread's token, pv = p/2 and gv = g/2 accumulators.
+// The bf16 results go to the warp's transpose stage as stage[channel][token-in-warp].
 template <bool HAS_BIAS, bool HAS_MASK>
-__device__ __forceinline__ void store_gated_group(const uint32_t (&pv)[32], const uint32_t (&gv)[32],
-                                                  const float* bias_p, const float* bias_g, float mval,
-                                                  __nv_bfloat16* base0, __nv_bfloat16* base1, long chan_stride) {
+__device__ __forceinline__ void gate_to_stage(const uint32_t (&pv)[32], const uint32_t (&gv)[32], const float* bias_p,
+                                              const float* bias_g, float mval, uint8_t* stage_lane) {
 #pragma unroll
   for (int e = 0; e < 32; ++e) {
     float pr = __uint_as_float(pv[e]);
@@ -80,8 +87,7 @@ __device__ __forceinline__ void store_gated_group(const uint32_t (&pv)[32], cons
     }
     float val = fmaf(pr, tanh_approx(ga), pr);
     if (HAS_MASK) val *= mval;
-    __nv_bfloat16* dst = (e < 16) ? base0 : base1;
-    dst[(e & 15) * chan_stride] = __float2bfloat16_rn(val);
+    *reinterpret_cast<__nv_bfloat16*>(stage_lane + e * kStagePitch) = __float2bfloat16_rn(val);
   }
 }
 
@@ -134,8 +140,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
   using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* a_tiles = tiles;                       // 2 x kABytes
-  uint8_t* w_tiles = tiles + 2 * C::kABytes;      // kWStages x kWStageBytes
+  uint8_t* a_tiles = tiles;                              // kABufs x kABytes
+  uint8_t* w_tiles = tiles + C::kABufs * C::kABytes;     // kWStages x kWStageBytes
   SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -170,9 +176,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   const uint64_t tmo = p.timeout_ns;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ weight producer (TMA from L2)
-    if (lane == 0) {
+  if (warp < kEpiWarp0) {
+    sm100::setmaxnreg_dec<40>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------- weight producer (TMA from L2)
       sm100::tma_prefetch_desc(&tmW);
       PipeState ps{0, 0};
       bool ok = true;
@@ -191,10 +198,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           }
         }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------- UMMA issuer
       constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
@@ -239,7 +244,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         }
         if (!ok) break;
         sm100::umma_commit(&ctl->x_empty[buf]);  // operand tile free once every MMA of the tile retired
-        if (++buf == 2) {
+        if (++buf == C::kABufs) {
           buf = 0;
           buf_phase ^= 1;
         }
@@ -247,11 +252,11 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     }
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
+    sm100::setmaxnreg_inc<112>();
     constexpr int CPR = D / 8;        // 16-byte chunks per row
     constexpr int RPP = 32 / CPR;     // rows one warp-wide load covers
     constexpr int ROWS_PER_WARP = 16;
-    constexpr int BATCH_ROWS = 8;     // rows in flight per warp
-    constexpr int PASSES = BATCH_ROWS / RPP;
+    constexpr int PASSES = ROWS_PER_WARP / RPP;
     const int lw = warp - kLnWarp0;
     const int chunk = lane % CPR;
     const int sub = lane / CPR;
@@ -266,6 +271,44 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
       const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+      // every row of this warp is requested before any is used: 16 x 512 B in flight per warp
+      uint4 raw[PASSES];
+#pragma unroll
+      for (int ps = 0; ps < PASSES; ++ps) {
+        const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
+        const int w = tc.w0 + r;
+        if (w < p.n_walk && !(p.debug_skip & 4)) {
+          raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
+        } else {
+          raw[ps] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      // normalise in registers while the tensor core still reads the previous tile
+#pragma unroll
+      for (int ps = 0; ps < PASSES; ++ps) {
+        float v[8];
+        v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
+        v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
+        v[4] = sm100::bf16_lo(raw[ps].z); v[5] = sm100::bf16_hi(raw[ps].z);
+        v[6] = sm100::bf16_lo(raw[ps].w); v[7] = sm100::bf16_hi(raw[ps].w);
+        float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+#pragma unroll
+        for (int o = CPR / 2; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float mean = s * (1.0f / D);
+        float q = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[e] -= mean;
+          q = fmaf(v[e], v[e], q);
+        }
+#pragma unroll
+        for (int o = CPR / 2; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+        const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
+        raw[ps].x = sm100::pack_bf16x2(fmaf(v[0] * rstd, gam[0], bet[0]), fmaf(v[1] * rstd, gam[1], bet[1]));
+        raw[ps].y = sm100::pack_bf16x2(fmaf(v[2] * rstd, gam[2], bet[2]), fmaf(v[3] * rstd, gam[3], bet[3]));
+        raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
+        raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
+      }
       bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -273,66 +316,37 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         break;
       }
       uint8_t* a_tile = a_tiles + buf * C::kABytes;
-#pragma unroll 1
-      for (int half = 0; half < ROWS_PER_WARP / BATCH_ROWS; ++half) {
-        uint4 raw[PASSES];
 #pragma unroll
-        for (int ps = 0; ps < PASSES; ++ps) {
-          const int r = lw * ROWS_PER_WARP + half * BATCH_ROWS + ps * RPP + sub;
-          const int w = tc.w0 + r;
-          if (w < p.n_walk && !(p.debug_skip & 4)) {
-            raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
-          } else {
-            raw[ps] = make_uint4(0, 0, 0, 0);
-          }
-        }
-#pragma unroll
-        for (int ps = 0; ps < PASSES; ++ps) {
-          const int r = lw * ROWS_PER_WARP + half * BATCH_ROWS + ps * RPP + sub;
-          float v[8];
-          v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
-          v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
-          v[4] = sm100::bf16_lo(raw[ps].z); v[5] = sm100::bf16_hi(raw[ps].z);
-          v[6] = sm100::bf16_lo(raw[ps].w); v[7] = sm100::bf16_hi(raw[ps].w);
-          float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-#pragma unroll
-          for (int o = CPR / 2; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          const float mean = s * (1.0f / D);
-          float q = 0.0f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            v[e] -= mean;
-            q = fmaf(v[e], v[e], q);
-          }
-#pragma unroll
-          for (int o = CPR / 2; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-          const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
-          uint4 o4;
-          o4.x = sm100::pack_bf16x2(fmaf(v[0] * rstd, gam[0], bet[0]), fmaf(v[1] * rstd, gam[1], bet[1]));
-          o4.y = sm100::pack_bf16x2(fmaf(v[2] * rstd, gam[2], bet[2]), fmaf(v[3] * rstd, gam[3], bet[3]));
-          o4.z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
-          o4.w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
-          // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
-          const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(a_tile + off) = o4;
-        }
+      for (int ps = 0; ps < PASSES; ++ps) {
+        const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
+        // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
+        const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(a_tile + off) = raw[ps];
       }
       sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
-      if (++buf == 2) {
+      if (++buf == C::kABufs) {
         buf = 0;
         buf_phase ^= 1;
       }
     }
-  } else if (warp >= kEpiWarp0) {
+  } else {
     // ------------------------------------------------------------ epilogue (8 warps)
+    sm100::setmaxnreg_inc<104>();
+    const int ew = warp - kEpiWarp0;
     const int quarter = warp & 3;
-    const int hh = (warp - kEpiWarp0) >> 2;  // which half of the chunk's columns
+    const int hh = ew >> 2;  // which half of the chunk's columns
     const int r = quarter * 32 + lane;
     const int d_loc_mask = (1 << p.d_loc_log2) - 1;
     const int d_loc_n = 1 << p.d_loc_log2;
     const long chan_stride = static_cast<long>(p.batch) * p.plane_elems;  // elements between channel planes
+    uint8_t* stage = ctl->stage[ew];
+    uint8_t* stage_lane = stage + lane * 2;
+    // read side of the transpose: this lane moves channel (8j + lane%8), tokens [8*(lane/8), +8) of the warp
+    const int l7 = lane & 7;
+    const int tb = lane >> 3;
+    const uint8_t* stage_rd = stage + l7 * kStagePitch + tb * 16;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -350,7 +364,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
-      const long dst_tok = p.dst_base + tc.line * p.dst_line + w;
+      // first token this lane stores (8 consecutive tokens, 16 bytes) and whether it exists
+      const int w_st = tc.w0 + quarter * 32 + tb * 8;
+      const bool st_valid = w_st < p.n_walk && !(p.debug_skip & 1);  // n_walk % 8 == 0: all 8 or none
+      const long dst_tok = p.dst_base + tc.line * p.dst_line + w_st;
       for (int c = 0; c < kNumChunks; ++c) {
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
         ok = __all_sync(0xffffffffu, ok);
@@ -371,25 +388,27 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
             sm100::tmem_ld_32x32b_x32(trow + col0, pv);
             sm100::tmem_ld_32x32b_x32(trow + C::CH + col0, gv);
             sm100::tmem_ld_wait();
-            if (valid && !(p.debug_skip & 1)) {
-              const float* bias_p = p.bias + c * D + col0;
-              const float* bias_g = bias_p + C::CH;
+            const float* bias_p = p.bias + c * D + col0;
+            const float* bias_g = bias_p + C::CH;
+            if (p.has_bias) {
+              if (p.mask_kind != 0) gate_to_stage<true, true>(pv, gv, bias_p, bias_g, mval, stage_lane);
+              else gate_to_stage<true, false>(pv, gv, bias_p, bias_g, mval, stage_lane);
+            } else {
+              if (p.mask_kind != 0) gate_to_stage<false, true>(pv, gv, bias_p, bias_g, mval, stage_lane);
+              else gate_to_stage<false, false>(pv, gv, bias_p, bias_g, mval, stage_lane);
+            }
+            __syncwarp();
+            if (st_valid) {
               const int d0 = (c & 1) * C::CH + col0;  // first channel of the group inside the a (or b) half
-              __nv_bfloat16* base[2];
 #pragma unroll
-              for (int k = 0; k < 2; ++k) {
-                const int d = d0 + 16 * k;
+              for (int j = 0; j < 4; ++j) {
+                const int d = d0 + 8 * j + l7;
                 const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
-                base[k] = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
-              }
-              if (p.has_bias) {
-                if (p.mask_kind != 0) store_gated_group<true, true>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
-                else store_gated_group<true, false>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
-              } else {
-                if (p.mask_kind != 0) store_gated_group<false, true>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
-                else store_gated_group<false, false>(pv, gv, bias_p, bias_g, mval, base[0], base[1], chan_stride);
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage_rd + j * 8 * kStagePitch);
               }
             }
+            __syncwarp();  // the stage is rewritten by the next group
           }
         } else {
           // output-gate chunk: sigmoid only, token-major local store
@@ -417,6 +436,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         }
       }
     }
+    (void)chan_stride;
   }
 
   // ------------------------------------------------------------------ teardown

@@ -10,13 +10,16 @@
 // The LayerNorm is folded algebraically so the channel-major tile never has to be transposed or
 // rewritten:   LN(x) W^T + b  =  rstd * ( x (gamma .* W)^T  -  mean * c )  +  d ,
 //     c[n] = sum_k bf16(gamma_k W[n,k]),   d[n] = sum_k beta_k W[n,k] + b[n]        (packed once).
-// The raw tile is the A operand as it lies in memory: TMA brings (64 channels x 64 tokens) boxes
-// with the 128-byte swizzle along TOKENS, and the tensor core reads them through an MN-major
-// (token-major) shared-memory descriptor.  Eight statistics warps read the same staged boxes and
+// The GEMM is issued transposed -- acc[n][m] = sum_k W'[n][k] tri[k][m] -- so that TMEM lanes are
+// output CHANNELS and columns are tokens: an epilogue warp then touches 32 consecutive channels of
+// one token per instruction (64 contiguous bytes of the token-major gate / out rows) instead of 32
+// different rows.  The raw tile is the B operand exactly as it lies in memory: TMA brings
+// (64 channels x 64 tokens) boxes with the 128-byte swizzle along TOKENS, and the tensor core
+// reads them through an MN-major (token-major) shared-memory descriptor.  Eight statistics warps read the same staged boxes and
 // reduce per-token mean / M2 (two-pass per 16 channels, Chan-merged), so the tile is fetched from
 // HBM exactly once, asynchronously, through a 5..8 stage ring.  gamma .* W stays resident in
-// shared memory.  Eight epilogue warps prefetch their slice of the gate, apply
-// rstd * acc + (-mean*rstd) * c + d, multiply by the gate and store 16-byte vectors token-major.
+// shared memory.  Eight epilogue warps (one channel per lane) apply
+// rstd[m] * acc + (-mean[m]*rstd[m]) * c[n] + d[n], multiply by the gate and store token-major.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -56,7 +59,6 @@ struct SmemCtl {
   volatile uint32_t armed[Cfg<D>::kStages];
   alignas(16) float2 red[2][4][BM];   // [tile parity][channel subgroup][token] = (mean, M2) over D/4 channels
   float2 stat[2][BM];     // [accumulator][token] = (rstd, -mean * rstd)
-  float2 cd[D];           // (c[n], d[n])
 };
 
 template <int D>
@@ -106,7 +108,6 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
   }
-  for (int i = threadIdx.x; i < D; i += kThreads) ctl->cd[i] = reinterpret_cast<const float2*>(p.cd)[i];
   if (warp == 2) {
     sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
     sm100::tmem_relinquish();
@@ -152,8 +153,9 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
     if (lane == 0 && my_tiles > 0) {
-      // A: token-major (MN-major) raw tile, B: K-major folded weights
-      const uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D) | (1u << 15);
+      // A: folded weights, K-major, one 128-channel M tile at a time; B: raw tile, token-major (MN-major)
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(128, BM) | (1u << 16);
+      constexpr int MT = D / 128;  // M tiles (output channels / 128)
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0;
       bool ok = sm100::mbar_wait(&ctl->w_full, 0, abort_flag, tmo);
@@ -176,13 +178,16 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             break;
           }
           sm100::tcgen05_fence_after_sync();
-          const uint32_t a_addr = sm100::smem_u32(ring + ps.stage * kStageBytes);
+          const uint32_t b_addr = sm100::smem_u32(ring + ps.stage * kStageBytes);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            // 16 channels per MMA = two 8-channel groups of 1024 B
-            const uint64_t da = sm100::umma_desc_mnmajor_sw128(a_addr + k4 * 2048, lbo, sbo);
-            const uint64_t db = sm100::umma_desc_kmajor_sw128(w_addr + kb * C::kWBlockBytes) + 2 * k4;
-            sm100::umma_bf16_ss(d_tmem, da, db, idesc, (kb | k4) != 0);
+          for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              // weights: 128 rows x 128 B per M tile inside the K block; tile: 16 channels per MMA = 2 KB
+              const uint64_t da = sm100::umma_desc_kmajor_sw128(w_addr + kb * C::kWBlockBytes + mt * 128 * 128) + 2 * k4;
+              const uint64_t db = sm100::umma_desc_mnmajor_sw128(b_addr + k4 * 2048, lbo, sbo);
+              sm100::umma_bf16_ss(d_tmem + mt * BM, da, db, idesc, (kb | k4) != 0);
+            }
           }
           sm100::umma_commit(&ctl->empty[ps.stage]);
           ps.advance(C::kStages);
@@ -302,59 +307,61 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     }
   } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------ epilogue (8 warps)
+    // TMEM lane = output channel, column = token.  D = 256: warps 4-7 take channels 0-127, warps
+    // 8-11 channels 128-255, all 128 tokens each.  D = 128: both sets take all channels and split
+    // the tokens 64 / 64.
     const int quarter = warp & 3;
-    const int hh = (warp - kEpiWarp0) >> 2;  // which half of the output columns
-    const int r = quarter * 32 + lane;
-    constexpr int COLS = D / 2;
-    constexpr int NV = COLS / 8;
+    const int set = (warp - kEpiWarp0) >> 2;
+    constexpr int MT = D / 128;
+    const int mt = (MT == 2) ? set : 0;
+    constexpr int NTOK = (MT == 2) ? BM : BM / 2;     // tokens this warp handles
+    const int tok0 = (MT == 2) ? 0 : set * NTOK;
+    const int n = mt * 128 + quarter * 32 + lane;      // this lane's output channel
+    const float2 cdn = reinterpret_cast<const float2*>(p.cd)[n];
+    const __nv_bfloat16* gate = static_cast<const __nv_bfloat16*>(p.gate) + n;
+    __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.out) + n;
+    const bool skip_ld = (p.debug_skip & 2) != 0, skip_st = (p.debug_skip & 4) != 0;
     uint32_t acc = 0, acc_phase = 0;
     for (long it = 0; it < my_tiles; ++it) {
-      const long t = blockIdx.x + it * gridDim.x;
-      const long m = t * BM + r;
-      const bool valid = m < p.rows;
-      // the gate slice is fetched before the accumulator is ready: its latency hides behind the wait
-      uint4 gt[NV];
-      if (valid && !(p.debug_skip & 2)) {
-        const uint8_t* gp = static_cast<const uint8_t*>(p.gate) + (m * D + hh * COLS) * 2;
+      const long m0 = (blockIdx.x + it * gridDim.x) * BM + tok0;
+      const int nvalid = static_cast<int>(p.rows - m0 < NTOK ? (p.rows - m0 > 0 ? p.rows - m0 : 0) : NTOK);
+      // gate values of the first 16 tokens are requested before the accumulator is ready
+      uint16_t gcur[16], gnext[16];
 #pragma unroll
-        for (int q = 0; q < NV; ++q) gt[q] = ldg_nc_v4(gp + q * 16);
-      } else {
-#pragma unroll
-        for (int q = 0; q < NV; ++q) gt[q] = make_uint4(0, 0, 0, 0);
-      }
+      for (int e = 0; e < 16; ++e)
+        gcur[e] = (e < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + e) * D)) : uint16_t(0);
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = ok && sm100::mbar_wait(&ctl->stats_ready[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        report_timeout(p.status, kKernelOutProj, 2, static_cast<int>(t));
+        report_timeout(p.status, kKernelOutProj, 2, static_cast<int>(it));
         break;
       }
       sm100::tcgen05_fence_after_sync();
-      const float2 rs = ctl->stat[acc][r];  // (rstd, -mean * rstd)
-      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D + hh * COLS;
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + m * D + hh * COLS);
-#pragma unroll
-      for (int g = 0; g < COLS / 16; ++g) {
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D + mt * BM + tok0;
+      const float2* stat = &ctl->stat[acc][tok0];
+#pragma unroll 1
+      for (int g = 0; g < ((p.debug_skip & 8) ? 0 : NTOK / 16); ++g) {
         uint32_t pv[16];
         sm100::tmem_ld_32x32b_x16(trow + g * 16, pv);
-        sm100::tmem_ld_wait();
-        if (valid && !(p.debug_skip & 4)) {
+        if (g + 1 < NTOK / 16) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const uint4 gq = gt[g * 2 + q];
-            const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
-            uint32_t ow[4];
-#pragma unroll
-            for (int e2 = 0; e2 < 4; ++e2) {
-              const int e = q * 8 + e2 * 2;
-              const float4 cd2 = *reinterpret_cast<const float4*>(&ctl->cd[hh * COLS + g * 16 + e]);  // c0 d0 c1 d1
-              const float y0 = fmaf(__uint_as_float(pv[e]), rs.x, fmaf(rs.y, cd2.x, cd2.y));
-              const float y1 = fmaf(__uint_as_float(pv[e + 1]), rs.x, fmaf(rs.y, cd2.z, cd2.w));
-              ow[e2] = sm100::pack_bf16x2(y0 * sm100::bf16_lo(gw[e2]), y1 * sm100::bf16_hi(gw[e2]));
-            }
-            dst[g * 2 + q] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          for (int e = 0; e < 16; ++e) {
+            const int m = (g + 1) * 16 + e;
+            gnext[e] = (m < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + m) * D)) : uint16_t(0);
           }
         }
+        sm100::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int m = g * 16 + e;
+          const float2 rs = stat[m];  // (rstd, -mean * rstd), same address for every lane
+          const float y = fmaf(__uint_as_float(pv[e]), rs.x, fmaf(rs.y, cdn.x, cdn.y));
+          const float gv = __uint_as_float(static_cast<uint32_t>(gcur[e]) << 16);
+          if (m < nvalid && !skip_st) outp[(m0 + m) * D] = __float2bfloat16_rn(y * gv);
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) gcur[e] = gnext[e];
       }
       sm100::tcgen05_fence_before_sync();
       __syncwarp();

@@ -231,6 +231,11 @@ __global__ void pack_out_weights_kernel(int d, const __nv_bfloat16* w_out, const
 
 }  // namespace
 
+namespace trimul {
+// Lets other translation units of the library leave a message in the slot trimul_sm100_last_error reads.
+void set_last_error(const char* msg) { fail(0, "%s", msg); }
+}  // namespace trimul
+
 extern "C" {
 
 const char* trimul_sm100_last_error(void) { return g_err; }
@@ -430,7 +435,7 @@ int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, c
   a.eps = geom->eps;
   a.D = D;
   a.rows = d.rows;
-  a.debug_skip = (debug_skip_bits() >> 4) & 7;
+  a.debug_skip = (debug_skip_bits() >> 4) & 15;
   a.mn_swap = (debug_skip_bits() >> 8) & 1;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
