@@ -23,6 +23,7 @@ ERR_UNSUPPORTED_SHAPE = -4
 MASK_NONE, MASK_BF16, MASK_FP32, MASK_U8 = 0, 1, 2, 3
 OUTGOING, INCOMING = 0, 1
 MAX_PEERS = 8
+STATIC_SCRATCH_BYTES = 32 << 20
 
 #: every symbol include/trimul_sm100.h declares; the CPU test-suite checks the library exports them
 EXPORTED_SYMBOLS = (
@@ -36,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "trimul_sm100_tri_contract",
     "trimul_sm100_ln_out_proj",
     "trimul_sm100_forward",
+    "trimul_sm100_forward_static",
     "trimul_sm100_peer_signal",
     "trimul_sm100_peer_wait",
 )
@@ -108,6 +110,9 @@ def load():
         lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, vp, f32p, vp, vp, u64, vp]
         lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, vp, f32p,
                                              vp, vp, vp, vp, vp, u64, vp]
+        lib.trimul_sm100_forward_static.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, vp, f32p,
+                                                    vp, vp, u64, vp]
+        lib.trimul_sm100_forward_static.restype = C.c_int
         lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, vp]
         lib.trimul_sm100_peer_wait.argtypes = [vp, i32, u64, vp, u64, vp]
         for name in ("trimul_sm100_query", "trimul_sm100_workspace", "trimul_sm100_pack_weights",

@@ -192,6 +192,23 @@ def forward_single(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, w_fol
     _lib.check(rc, "trimul_sm100_forward")
 
 
+def forward_static(geom, x, mask, ln_in_w, ln_in_b, w_packed, bias_packed, w_fold, cd, out, status,
+                   timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+    """The cp=1 chain with the library's built-in scratch array instead of caller buffers.
+
+    For callers that cannot allocate device memory: no tensor is created here and the library
+    allocates nothing.  Shapes need ``8 * batch * n * n * d <= STATIC_SCRATCH_BYTES`` (32 MiB);
+    larger ones raise ``ValueError``.  Calls that overlap on the GPU share the one array and race.
+    """
+    _require(x, torch.bfloat16, "x")
+    _require(out, torch.bfloat16, "out")
+    mptr, mkind = _mask_args(mask)
+    rc = _lib.load().trimul_sm100_forward_static(C.byref(geom), _ptr(x), mptr, mkind, _ptr(ln_in_w), _ptr(ln_in_b),
+                                                 _ptr(w_packed), _ptr(bias_packed), _ptr(w_fold), _ptr(cd), _ptr(out),
+                                                 _ptr(status), int(timeout_ns), _stream())
+    _lib.check(rc, "trimul_sm100_forward_static")
+
+
 def peer_signal(flag_peer_ptrs: Sequence[int], slot: int) -> None:
     """Add 1 to counter ``slot`` on every rank of the cp group (enqueued on the current stream)."""
     rc = _lib.load().trimul_sm100_peer_signal(_ptr_array(flag_peer_ptrs), len(flag_peer_ptrs), int(slot), _stream())

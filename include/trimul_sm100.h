@@ -171,6 +171,24 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
                          void* gate, void* out, trimul_status_t* status, uint64_t timeout_ns,
                          trimul_stream_t stream);
 
+/* Single-GPU forward for callers that cannot allocate device memory (no counterpart in the
+ * reference, which always allocates its own buffers).  Same arguments as trimul_sm100_forward minus
+ * the three scratch buffers: the a|b planes, the contraction result and the gate live in a
+ * TRIMUL_STATIC_SCRATCH_BYTES array built into the library, resident on every GPU that loads it.
+ * Meant for hosts whose memory pool already owns the whole device, sandboxed plugins that may not call
+ * allocation APIs, and latency-critical loops that cannot afford cudaMalloc's device synchronisation.
+ * No cudaMalloc / cudaFree / allocating library call is made.  Limits: cp0 = cp1 = 1 and
+ * 8 * batch * n * n * d <= TRIMUL_STATIC_SCRATCH_BYTES, otherwise TRIMUL_ERR_UNSUPPORTED_SHAPE with a
+ * message in trimul_sm100_last_error().  All calls on a device share the one array: calls that overlap on
+ * the GPU race.  The array keeps the previous call's contents; the forward overwrites everything it
+ * reads, so nothing is cleared.  The first call on a device looks up the array's device address -- make
+ * it outside any stream capture. */
+#define TRIMUL_STATIC_SCRATCH_BYTES (32u << 20)
+int trimul_sm100_forward_static(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
+                                const float* ln_in_w, const float* ln_in_b, const void* w_packed,
+                                const float* bias_packed, const void* w_fold, const float* cd, void* out,
+                                trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+
 /* Rank-to-rank ordering of the fused reshards.  Every rank owns a symmetric array of 16 uint64
  * counters (zeroed once).  `peer_signal` adds 1 to counter `slot` on every rank listed in
  * flag_peers[0..cp) (release, system scope) and is enqueued after the kernel whose stores it
