@@ -72,13 +72,13 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return t;
 }
 
-// One 32-channel group of a gated chunk: this thread's token, pv = p/2 and gv = g/2 accumulators.
+// Sixteen channels of a gated chunk for this thread's token: pv = p/2 and gv = g/2 accumulators.
 // The bf16 results go to the warp's transpose stage as stage[channel][token-in-warp].
 template <bool HAS_BIAS, bool HAS_MASK>
-__device__ __forceinline__ void gate_to_stage(const uint32_t (&pv)[32], const uint32_t (&gv)[32], const float* bias_p,
-                                              const float* bias_g, float mval, uint8_t* stage_lane) {
+__device__ __forceinline__ void gate_to_stage16(const uint32_t (&pv)[16], const uint32_t (&gv)[16], const float* bias_p,
+                                                const float* bias_g, float mval, uint8_t* stage_rows) {
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
+  for (int e = 0; e < 16; ++e) {
     float pr = __uint_as_float(pv[e]);
     float ga = __uint_as_float(gv[e]);
     if (HAS_BIAS) {
@@ -87,14 +87,26 @@ __device__ __forceinline__ void gate_to_stage(const uint32_t (&pv)[32], const ui
     }
     float val = fmaf(pr, tanh_approx(ga), pr);
     if (HAS_MASK) val *= mval;
-    *reinterpret_cast<__nv_bfloat16*>(stage_lane + e * kStagePitch) = __float2bfloat16_rn(val);
+    *reinterpret_cast<__nv_bfloat16*>(stage_rows + e * kStagePitch) = __float2bfloat16_rn(val);
+  }
+}
+
+__device__ __forceinline__ void gate_to_stage16_dispatch(int has_bias, bool has_mask, const uint32_t (&pv)[16],
+                                                         const uint32_t (&gv)[16], const float* bias_p,
+                                                         const float* bias_g, float mval, uint8_t* stage_rows) {
+  if (has_bias) {
+    if (has_mask) gate_to_stage16<true, true>(pv, gv, bias_p, bias_g, mval, stage_rows);
+    else gate_to_stage16<true, false>(pv, gv, bias_p, bias_g, mval, stage_rows);
+  } else {
+    if (has_mask) gate_to_stage16<false, true>(pv, gv, bias_p, bias_g, mval, stage_rows);
+    else gate_to_stage16<false, false>(pv, gv, bias_p, bias_g, mval, stage_rows);
   }
 }
 
 template <bool HAS_BIAS>
-__device__ __forceinline__ void store_gate_group(const uint32_t (&gv)[32], const float* bias_g, uint4* dst) {
+__device__ __forceinline__ void gate16_to_global(const uint32_t (&gv)[16], const float* bias_g, uint4* dst) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
+  for (int q = 0; q < 2; ++q) {
     float s[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -340,7 +352,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     const int r = quarter * 32 + lane;
     const int d_loc_mask = (1 << p.d_loc_log2) - 1;
     const int d_loc_n = 1 << p.d_loc_log2;
-    const long chan_stride = static_cast<long>(p.batch) * p.plane_elems;  // elements between channel planes
     uint8_t* stage = ctl->stage[ew];
     uint8_t* stage_lane = stage + lane * 2;
     // read side of the transpose: this lane moves channel (8j + lane%8), tokens [8*(lane/8), +8) of the warp
@@ -377,53 +388,74 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         }
         sm100::tcgen05_fence_after_sync();
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
+        // TMEM reads are software-pipelined: the load of the next 16 columns is in flight while the
+        // current 16 are processed (tcgen05.wait::ld is placed after the work on the other buffer).
         if (c < 4) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
           const int h = c >> 1;
-          constexpr int GROUPS = C::CH / 2 / 32;
-#pragma unroll 1
-          for (int g = 0; g < GROUPS; ++g) {
-            const int col0 = hh * (C::CH / 2) + g * 32;
-            uint32_t pv[32], gv[32];
-            sm100::tmem_ld_32x32b_x32(trow + col0, pv);
-            sm100::tmem_ld_32x32b_x32(trow + C::CH + col0, gv);
-            sm100::tmem_ld_wait();
-            const float* bias_p = p.bias + c * D + col0;
-            const float* bias_g = bias_p + C::CH;
-            if (p.has_bias) {
-              if (p.mask_kind != 0) gate_to_stage<true, true>(pv, gv, bias_p, bias_g, mval, stage_lane);
-              else gate_to_stage<true, false>(pv, gv, bias_p, bias_g, mval, stage_lane);
-            } else {
-              if (p.mask_kind != 0) gate_to_stage<false, true>(pv, gv, bias_p, bias_g, mval, stage_lane);
-              else gate_to_stage<false, false>(pv, gv, bias_p, bias_g, mval, stage_lane);
-            }
-            __syncwarp();
-            if (st_valid) {
-              const int d0 = (c & 1) * C::CH + col0;  // first channel of the group inside the a (or b) half
+          constexpr int NS = C::CH / 2 / 16;   // 16-channel sub-groups this warp handles
+          const int colw = hh * (C::CH / 2);
+          const float* bias_p0 = p.bias + c * D + colw;
+          const bool has_mask = p.mask_kind != 0;
+          uint32_t pa[16], ga[16], pb[16], gb[16];
+          sm100::tmem_ld_32x32b_x16(trow + colw, pa);
+          sm100::tmem_ld_32x32b_x16(trow + C::CH + colw, ga);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int d = d0 + 8 * j + l7;
-                const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
-                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage_rd + j * 8 * kStagePitch);
+          for (int sg = 0; sg < NS; ++sg) {
+            sm100::tmem_ld_wait();
+            if (sg + 1 < NS) {
+              if ((sg & 1) == 0) {
+                sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, pb);
+                sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + (sg + 1) * 16, gb);
+              } else {
+                sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, pa);
+                sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + (sg + 1) * 16, ga);
               }
             }
-            __syncwarp();  // the stage is rewritten by the next group
+            uint8_t* rows = stage_lane + (sg & 1) * 16 * kStagePitch;
+            if ((sg & 1) == 0) {
+              gate_to_stage16_dispatch(p.has_bias, has_mask, pa, ga, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval, rows);
+            } else {
+              gate_to_stage16_dispatch(p.has_bias, has_mask, pb, gb, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval, rows);
+              // 32 channels are staged: transpose out, 16 bytes (8 tokens of one channel) per lane and store
+              __syncwarp();
+              if (st_valid) {
+                const int d0 = (c & 1) * C::CH + colw + (sg - 1) * 16;  // first channel of the 32 inside the a (or b) half
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int d = d0 + 8 * j + l7;
+                  const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
+                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
+                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage_rd + j * 8 * kStagePitch);
+                }
+              }
+              __syncwarp();  // the stage is rewritten by the next pair of sub-groups
+            }
           }
         } else {
           // output-gate chunk: sigmoid only, token-major local store
-          constexpr int GROUPS = D / 2 / 32;
-#pragma unroll 1
-          for (int g = 0; g < GROUPS; ++g) {
-            const int col0 = hh * (D / 2) + g * 32;
-            uint32_t gv[32];
-            sm100::tmem_ld_32x32b_x32(trow + col0, gv);
+          constexpr int NS = D / 2 / 16;
+          const int colw = hh * (D / 2);
+          const float* bias_g0 = p.bias + 4 * D + colw;
+          uint4* dst0 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gate_out) + srow * D + colw);
+          const bool do_store = valid && !(p.debug_skip & 2);
+          uint32_t ga[16], gb[16];
+          sm100::tmem_ld_32x32b_x16(trow + colw, ga);
+#pragma unroll
+          for (int sg = 0; sg < NS; ++sg) {
             sm100::tmem_ld_wait();
-            if (valid && !(p.debug_skip & 2)) {
-              const float* bias_g = p.bias + 4 * D + col0;
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gate_out) + srow * D + col0);
-              if (p.has_bias) store_gate_group<true>(gv, bias_g, dst);
-              else store_gate_group<false>(gv, bias_g, dst);
+            if (sg + 1 < NS) {
+              if ((sg & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, gb);
+              else sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, ga);
+            }
+            if (do_store) {
+              if ((sg & 1) == 0) {
+                if (p.has_bias) gate16_to_global<true>(ga, bias_g0 + sg * 16, dst0 + sg * 2);
+                else gate16_to_global<false>(ga, bias_g0 + sg * 16, dst0 + sg * 2);
+              } else {
+                if (p.has_bias) gate16_to_global<true>(gb, bias_g0 + sg * 16, dst0 + sg * 2);
+                else gate16_to_global<false>(gb, bias_g0 + sg * 16, dst0 + sg * 2);
+              }
             }
           }
         }
@@ -436,7 +468,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         }
       }
     }
-    (void)chan_stride;
   }
 
   // ------------------------------------------------------------------ teardown

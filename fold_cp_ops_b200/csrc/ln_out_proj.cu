@@ -340,28 +340,34 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       sm100::tcgen05_fence_after_sync();
       const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D + mt * BM + tok0;
       const float2* stat = &ctl->stat[acc][tok0];
-#pragma unroll 1
-      for (int g = 0; g < ((p.debug_skip & 8) ? 0 : NTOK / 16); ++g) {
-        uint32_t pv[16];
-        sm100::tmem_ld_32x32b_x16(trow + g * 16, pv);
-        if (g + 1 < NTOK / 16) {
+      // TMEM reads and gate loads are software-pipelined one 16-token group ahead
+      if (!(p.debug_skip & 8)) {
+        uint32_t pa[16], pb[16];
+        sm100::tmem_ld_32x32b_x16(trow, pa);
+#pragma unroll
+        for (int g = 0; g < NTOK / 16; ++g) {
+          sm100::tmem_ld_wait();
+          if (g + 1 < NTOK / 16) {
+            if ((g & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pb);
+            else sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pa);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int m = (g + 1) * 16 + e;
+              gnext[e] = (m < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + m) * D)) : uint16_t(0);
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const int m = (g + 1) * 16 + e;
-            gnext[e] = (m < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + m) * D)) : uint16_t(0);
+            const int m = g * 16 + e;
+            const float2 rs = stat[m];  // (rstd, -mean * rstd), same address for every lane
+            const float accv = __uint_as_float((g & 1) == 0 ? pa[e] : pb[e]);
+            const float y = fmaf(accv, rs.x, fmaf(rs.y, cdn.x, cdn.y));
+            const float gv = __uint_as_float(static_cast<uint32_t>(gcur[e]) << 16);
+            if (m < nvalid && !skip_st) outp[(m0 + m) * D] = __float2bfloat16_rn(y * gv);
           }
-        }
-        sm100::tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int m = g * 16 + e;
-          const float2 rs = stat[m];  // (rstd, -mean * rstd), same address for every lane
-          const float y = fmaf(__uint_as_float(pv[e]), rs.x, fmaf(rs.y, cdn.x, cdn.y));
-          const float gv = __uint_as_float(static_cast<uint32_t>(gcur[e]) << 16);
-          if (m < nvalid && !skip_st) outp[(m0 + m) * D] = __float2bfloat16_rn(y * gv);
+          for (int e = 0; e < 16; ++e) gcur[e] = gnext[e];
         }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) gcur[e] = gnext[e];
       }
       sm100::tcgen05_fence_before_sync();
       __syncwarp();
