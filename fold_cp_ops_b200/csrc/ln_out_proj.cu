@@ -66,6 +66,11 @@ constexpr int smem_bytes() {
   return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
+__device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
+  uint32_t v;
+  asm volatile("{\n\t.reg .b16 h;\n\tld.global.nc.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -325,11 +330,18 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     for (long it = 0; it < my_tiles; ++it) {
       const long m0 = (blockIdx.x + it * gridDim.x) * BM + tok0;
       const int nvalid = static_cast<int>(p.rows - m0 < NTOK ? (p.rows - m0 > 0 ? p.rows - m0 : 0) : NTOK);
-      // gate values of the first 16 tokens are requested before the accumulator is ready
-      uint16_t gcur[16], gnext[16];
+      // gate values of the first 16 tokens are requested before the accumulator is ready.  Loads are
+      // unconditional (a token index past the end is clamped to the last valid one) so that all 16
+      // are in flight together; only the stores are predicated.
+      const int last = nvalid - 1;
+      const bool do_ld = nvalid > 0 && !skip_ld;
+      uint32_t gcur[16], gnext[16];
 #pragma unroll
-      for (int e = 0; e < 16; ++e)
-        gcur[e] = (e < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + e) * D)) : uint16_t(0);
+      for (int e = 0; e < 16; ++e) gcur[e] = gnext[e] = 0;
+      if (do_ld) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) gcur[e] = ldg_nc_u16(gate + (m0 + (e < last ? e : last)) * D);
+      }
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = ok && sm100::mbar_wait(&ctl->stats_ready[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
@@ -350,10 +362,12 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           if (g + 1 < NTOK / 16) {
             if ((g & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pb);
             else sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pa);
+            if (do_ld) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int m = (g + 1) * 16 + e;
-              gnext[e] = (m < nvalid && !skip_ld) ? __ldg(reinterpret_cast<const uint16_t*>(gate + (m0 + m) * D)) : uint16_t(0);
+              for (int e = 0; e < 16; ++e) {
+                const int m = (g + 1) * 16 + e;
+                gnext[e] = ldg_nc_u16(gate + (m0 + (m < last ? m : last)) * D);
+              }
             }
           }
 #pragma unroll
@@ -362,7 +376,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const float2 rs = stat[m];  // (rstd, -mean * rstd), same address for every lane
             const float accv = __uint_as_float((g & 1) == 0 ? pa[e] : pb[e]);
             const float y = fmaf(accv, rs.x, fmaf(rs.y, cdn.x, cdn.y));
-            const float gv = __uint_as_float(static_cast<uint32_t>(gcur[e]) << 16);
+            const float gv = __uint_as_float(gcur[e] << 16);
             if (m < nvalid && !skip_st) outp[(m0 + m) * D] = __float2bfloat16_rn(y * gv);
           }
 #pragma unroll
