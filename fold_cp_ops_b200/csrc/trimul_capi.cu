@@ -395,9 +395,22 @@ int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, v
   a.nj_loc = d.nj_loc;
   a.cp1 = geom->cp1;
   a.chan_offset = geom->rank * d.d_loc;
+  trimul::TriOutMaps out_maps;
+  memset(&out_maps, 0, sizeof(out_maps));
+  {
+    // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)
+    const uint64_t odims[3] = {static_cast<uint64_t>(d.nj_loc), static_cast<uint64_t>(d.ni_loc),
+                               static_cast<uint64_t>(geom->d) * geom->batch};
+    const uint64_t ostr[2] = {static_cast<uint64_t>(d.nj_loc) * 2, static_cast<uint64_t>(d.nj_loc) * d.ni_loc * 2};
+    const uint32_t obox[3] = {64, 32, 1};
+    for (int s = 0; s < d.cp; ++s) {
+      rc = make_tmap(&out_maps.map[s], tri_peers[s], 3, odims, ostr, obox);
+      if (rc != TRIMUL_OK) return rc;
+    }
+  }
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_tri_contract(tmA, tmB, a, num_sms_current(), stream);
+  cudaError_t e = trimul::launch_tri_contract(tmA, tmB, out_maps, a, num_sms_current(), stream);
   if (e != cudaSuccess) return cuda_fail(e, "tri_contract launch");
   return TRIMUL_OK;
 }

@@ -64,9 +64,14 @@ struct TriContractArgs {
   uint64_t timeout_ns;
 };
 
+// One store descriptor per destination rank: rank s's `tri` buffer as (nj_loc, ni_loc, D*B), box (64, 32, 1).
+struct TriOutMaps {
+  CUtensorMap map[kMaxPeers];
+};
+
 int tri_contract_smem_bytes();
-cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, const TriContractArgs& args,
-                                int num_sms, cudaStream_t stream);
+cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, const TriOutMaps& out_maps,
+                                const TriContractArgs& args, int num_sms, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // K_C  output LayerNorm + output projection, gated
