@@ -66,6 +66,24 @@ constexpr int smem_bytes() {
   return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
+// Optional device timeline of CTA 0 (profiling aid): (globaltimer << 8 | event id) records.  Each
+// tracing thread owns a private region (role * cap) and a private counter, so an event costs one
+// fire-and-forget store.
+__device__ unsigned long long* g_trace_buf = nullptr;
+__device__ unsigned int g_trace_cap = 0;  // records per role
+struct Tracer {
+  unsigned long long* base;
+  unsigned int n, cap;
+  __device__ __forceinline__ void init(int role) {
+    base = (g_trace_buf != nullptr && blockIdx.x == 0) ? g_trace_buf + static_cast<size_t>(role) * g_trace_cap : nullptr;
+    n = 0;
+    cap = g_trace_cap;
+  }
+  __device__ __forceinline__ void ev(int id) {
+    if (base != nullptr && n < cap) base[n++] = (sm100::globaltimer_ns() << 8) | static_cast<unsigned long long>(id & 0xff);
+  }
+};
+
 __device__ __forceinline__ float tanh_approx(float x) {
   float t;
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
@@ -213,6 +231,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- UMMA issuer
       constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
+      Tracer tr;
+      tr.init(0);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
@@ -222,6 +242,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           break;
         }
         sm100::tcgen05_fence_after_sync();
+        tr.ev(1);
         const uint32_t a_addr = sm100::smem_u32(a_tiles + buf * C::kABytes);
         for (int c = 0; c < kNumChunks && ok; ++c) {
           if (!sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo)) {
@@ -230,6 +251,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
             break;
           }
           sm100::tcgen05_fence_after_sync();
+          tr.ev(2);
           const uint32_t d_tmem = tmem_base + acc * D;
           for (int kb = 0; kb < C::KB; ++kb) {
             if (!sm100::mbar_wait(&ctl->w_full[ps.stage], ps.phase, abort_flag, tmo)) {
@@ -249,6 +271,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           }
           if (!ok) break;
           sm100::umma_commit(&ctl->tmem_full[acc]);
+          tr.ev(3);
           if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1;
@@ -279,6 +302,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
       bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
     }
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    Tracer tr;
+    tr.init(1);
     uint32_t buf = 0, buf_phase = 0;
     for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
@@ -295,6 +320,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           raw[ps] = make_uint4(0, 0, 0, 0);
         }
       }
+      if (lw == 0 && lane == 0) tr.ev(6);
       // normalise in registers while the tensor core still reads the previous tile
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
@@ -321,12 +347,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
         raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
       }
+      if (lw == 0 && lane == 0) tr.ev(7);
       bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
         break;
       }
+      if (lw == 0 && lane == 0) tr.ev(8);
       uint8_t* a_tile = a_tiles + buf * C::kABytes;
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
@@ -338,6 +366,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
       sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
+      if (lw == 0 && lane == 0) tr.ev(9);
       if (++buf == C::kABufs) {
         buf = 0;
         buf_phase ^= 1;
@@ -358,6 +387,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     const int l7 = lane & 7;
     const int tb = lane >> 3;
     const uint8_t* stage_rd = stage + l7 * kStagePitch + tb * 16;
+    Tracer tr;
+    tr.init(2);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -387,6 +418,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           break;
         }
         sm100::tcgen05_fence_after_sync();
+        if (ew == 0 && lane == 0) tr.ev(4);
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
         // TMEM reads are software-pipelined: the load of the next 16 columns is in flight while the
         // current 16 are processed (tcgen05.wait::ld is placed after the work on the other buffer).
@@ -403,6 +435,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
             sm100::tmem_ld_wait();
+            if (ew == 0 && lane == 0) tr.ev(11);
             if (sg + 1 < NS) {
               if ((sg & 1) == 0) {
                 sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, pb);
@@ -419,6 +452,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
               gate_to_stage16_dispatch(p.has_bias, has_mask, pb, gb, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval, rows);
               // 32 channels are staged: transpose out, 16 bytes (8 tokens of one channel) per lane and store
               __syncwarp();
+              if (ew == 0 && lane == 0) tr.ev(12);
               if (st_valid) {
                 const int d0 = (c & 1) * C::CH + colw + (sg - 1) * 16;  // first channel of the 32 inside the a (or b) half
 #pragma unroll
@@ -430,6 +464,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
                 }
               }
               __syncwarp();  // the stage is rewritten by the next pair of sub-groups
+              if (ew == 0 && lane == 0) tr.ev(13);
             }
           }
         } else {
@@ -462,6 +497,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         sm100::tcgen05_fence_before_sync();
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+        if (ew == 0 && lane == 0) tr.ev(5);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -493,6 +529,16 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
+// Profiling aid: point the projection kernel's CTA-0 timeline at a device buffer of `cap` uint64
+// records (nullptr switches it off).  Not part of the C ABI.
+extern "C" int trimul_debug_set_gated_proj_trace(void* buf, unsigned int cap) {
+  unsigned long long* b = static_cast<unsigned long long*>(buf);
+  cap /= 3;  // three tracing roles share the buffer
+  if (cudaMemcpyToSymbol(g_trace_buf, &b, sizeof(b)) != cudaSuccess) return -1;
+  if (cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof(cap)) != cudaSuccess) return -1;
+  return 0;
+}
+
 int gated_proj_smem_bytes(int D) {
   if (D == 128) return smem_bytes<128>();
   if (D == 256) return smem_bytes<256>();

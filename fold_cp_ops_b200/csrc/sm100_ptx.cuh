@@ -82,6 +82,23 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the hardware may park the thread until the phase completes or
+// about `hint_ns` elapse, so a waiting warp does not burn issue slots its SM sub-partition shares
+// with the warps doing the work.
+__device__ __forceinline__ bool mbar_test_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` is a CTA-shared word any role sets when it gives up; every
 // waiter polls it so that one timeout drains the whole CTA instead of stranding the others.
 // Returns true when the phase completed, false on timeout/abort.

@@ -395,6 +395,7 @@ int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, v
   a.nj_loc = d.nj_loc;
   a.cp1 = geom->cp1;
   a.chan_offset = geom->rank * d.d_loc;
+  a.direct_stores = (debug_skip_bits() >> 9) & 1;
   trimul::TriOutMaps out_maps;
   memset(&out_maps, 0, sizeof(out_maps));
   {

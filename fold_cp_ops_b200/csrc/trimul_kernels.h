@@ -60,6 +60,7 @@ struct TriContractArgs {
   PeerPtrs out;
   int ni_loc, nj_loc, cp1;
   int chan_offset;
+  int direct_stores;  // diagnostic (TRIMUL_DEBUG_SKIP bit 9): skip the staged TMA stores, store from registers
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
