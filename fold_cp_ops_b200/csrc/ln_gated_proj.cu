@@ -12,10 +12,13 @@
 // registers, normalise them there (two-pass fp32 statistics), and write the bf16 operand tile into
 // shared memory in the K-major 128-byte-swizzle layout once the tensor core has released it;
 // weights stream through a four-stage TMA ring (they live in L2); one thread issues tcgen05.mma
-// for five N=D column chunks per tile into two TMEM accumulators; eight epilogue warps apply bias /
-// gate / mask, transpose 32-channel x 32-token blocks through a small per-warp shared-memory
-// stage, and store 16-byte vectors into the channel-major operand plane of the rank that owns
-// the channel (front all-to-all fused in the store; at cp=1 that rank is this GPU).
+// for five N=D column chunks per tile into two TMEM accumulators; sixteen epilogue warps (four per
+// TMEM lane quarter) apply bias / gate / mask, write 16-channel x 32-token blocks channel-major
+// into a small per-warp shared-memory stage, and hand each block to a TMA store into the
+// channel-major operand plane of the rank that owns the channels (front all-to-all fused in the
+// store; at cp=1 that rank is this GPU).  The output gate goes out the same way, token-major.
+// No epilogue thread issues a global store: scattered 16-byte stores from 512 threads cost this
+// kernel 40 % of its time, bulk stores of whole blocks are asynchronous and full-sector.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -24,15 +27,18 @@ namespace trimul {
 namespace {
 
 constexpr int BM = 128;
-// Five warpgroups: w0-3 control (w0 weight TMA, w1 MMA issue, w2 TMEM alloc), w4-11 epilogue,
-// w12-19 LayerNorm.  Launched at 96 registers per thread and rebalanced with setmaxnreg:
-// control 40, epilogue 104, LayerNorm 112 ((40 + 2*104 + 2*112) * 32 = 15104 <= 16384 per SMSP).
-constexpr int kThreads = 640;
+// Seven warpgroups: w0-3 control (w0 weight TMA, w1 MMA issue, w2 TMEM alloc), w4-19 epilogue,
+// w20-27 LayerNorm.  Launched at 72 registers per thread and rebalanced with setmaxnreg:
+// control 40, epilogue 64, LayerNorm 104 ((40 + 4*64 + 2*104) * 32 = 16128 <= 16384 per SMSP).
+constexpr int kEpiWarps = 16;
+constexpr int kLnWarps = 8;
 constexpr int kEpiWarp0 = 4;
-constexpr int kLnWarp0 = 12;
+constexpr int kLnWarp0 = kEpiWarp0 + kEpiWarps;
+constexpr int kThreads = (kLnWarp0 + kLnWarps) * 32;
 constexpr int kNumChunks = 5;            // a_lo, a_hi, b_lo, b_hi, gate
-constexpr int kStagePitch = 80;          // bytes per channel row of the transpose stage (64 + 16 pad)
-constexpr int kStageBytes = 32 * kStagePitch;
+constexpr int kStagePitch = 64;          // bytes per channel row of an a|b block: 32 tokens, dense (TMA box layout)
+constexpr int kBlockBytes = 16 * kStagePitch;   // one a|b block: 16 channels x 32 tokens
+constexpr int kStageBytes = 2 * kBlockBytes;    // per warp: two a|b blocks, or one 32-token x 32-channel gate block
 
 template <int D>
 struct Cfg {
@@ -58,7 +64,7 @@ struct SmemCtl {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kWStages];
-  alignas(16) uint8_t stage[8][kStageBytes];  // one transpose stage per epilogue warp
+  alignas(1024) uint8_t stage[kEpiWarps][kStageBytes];  // one transpose stage per epilogue warp
 };
 
 template <int D>
@@ -121,10 +127,15 @@ __device__ __forceinline__ void gate_to_stage16_dispatch(int has_bias, bool has_
   }
 }
 
+// Thirty-two output-gate channels of this thread's token: sigmoid, bf16, written as the token's
+// 64-byte row of the warp's gate block in the 64-byte-swizzle layout the TMA store expects
+// (16-byte slot index ^ ((row / 2) % 4)); conflict-free for 16-byte stores.
 template <bool HAS_BIAS>
-__device__ __forceinline__ void gate16_to_global(const uint32_t (&gv)[16], const float* bias_g, uint4* dst) {
+__device__ __forceinline__ void gate32_to_stage(const uint32_t (&gv)[32], const float* bias_g, uint8_t* stage, int row) {
+  uint8_t* row_ptr = stage + row * 64;
+  const int sw = (row >> 1) & 3;
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {
+  for (int q = 0; q < 4; ++q) {
     float s[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -137,7 +148,7 @@ __device__ __forceinline__ void gate16_to_global(const uint32_t (&gv)[16], const
     pk.y = sm100::pack_bf16x2(s[2], s[3]);
     pk.z = sm100::pack_bf16x2(s[4], s[5]);
     pk.w = sm100::pack_bf16x2(s[6], s[7]);
-    dst[q] = pk;
+    *reinterpret_cast<uint4*>(row_ptr + ((q ^ sw) << 4)) = pk;
   }
 }
 
@@ -166,7 +177,8 @@ __device__ __forceinline__ TileCoord decode_tile(long t, int tiles_per_line, int
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p) {
+gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ GatedOutMaps om,
+                  const GatedProjArgs p) {
   using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -187,10 +199,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
       ctl->armed[s] = 2;
     }
     for (int a = 0; a < 2; ++a) {
-      sm100::mbar_init(&ctl->xn_ready[a], 8);    // one arrive per LayerNorm warp
+      sm100::mbar_init(&ctl->xn_ready[a], kLnWarps);    // one arrive per LayerNorm warp
       sm100::mbar_init(&ctl->x_empty[a], 1);     // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_full[a], 1);   // tcgen05.commit
-      sm100::mbar_init(&ctl->tmem_empty[a], 8);  // one arrive per epilogue warp
+      sm100::mbar_init(&ctl->tmem_empty[a], kEpiWarps);  // one arrive per epilogue warp
     }
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
@@ -212,6 +224,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
       // ---------------------------------------------------------- weight producer (TMA from L2)
       sm100::tma_prefetch_desc(&tmW);
       PipeState ps{0, 0};
+      uint32_t n_loads = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int c = 0; c < kNumChunks && ok; ++c) {
@@ -221,9 +234,18 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
               ok = false;
               break;
             }
-            ctl->armed[ps.stage] = ps.phase;
-            sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], C::kWStageBytes);
-            sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes, &tmW, &ctl->w_full[ps.stage], kb * 64, c * D);
+            // profiling probes: bit 3 reuses stale stages after the first pass (no weight traffic),
+            // bit 4 reloads only every other stage (half the weight traffic); results are wrong
+            const bool skip_load = ((p.debug_skip & 8) && n_loads >= C::kWStages) ||
+                                   ((p.debug_skip & 16) && n_loads >= C::kWStages && (n_loads & 1));
+            ++n_loads;
+            if (skip_load) {
+              sm100::mbar_arrive(&ctl->w_full[ps.stage]);
+            } else {
+              ctl->armed[ps.stage] = ps.phase;
+              sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], C::kWStageBytes);
+              sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes, &tmW, &ctl->w_full[ps.stage], kb * 64, c * D);
+            }
             ps.advance(C::kWStages);
           }
         }
@@ -287,7 +309,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
     }
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
-    sm100::setmaxnreg_inc<112>();
+    sm100::setmaxnreg_inc<104>();
     constexpr int CPR = D / 8;        // 16-byte chunks per row
     constexpr int RPP = 32 / CPR;     // rows one warp-wide load covers
     constexpr int ROWS_PER_WARP = 16;
@@ -373,23 +395,19 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (8 warps)
-    sm100::setmaxnreg_inc<104>();
+    // ------------------------------------------------------------ epilogue (16 warps)
+    sm100::setmaxnreg_dec<64>();
     const int ew = warp - kEpiWarp0;
-    const int quarter = warp & 3;
-    const int hh = ew >> 2;  // which half of the chunk's columns
+    const int quarter = warp & 3;   // TMEM lane quarter this warp may read
+    const int part = ew >> 2;       // which quarter of the chunk's columns
     const int r = quarter * 32 + lane;
     const int d_loc_mask = (1 << p.d_loc_log2) - 1;
     const int d_loc_n = 1 << p.d_loc_log2;
     uint8_t* stage = ctl->stage[ew];
     uint8_t* stage_lane = stage + lane * 2;
-    // read side of the transpose: this lane moves channel (8j + lane%8), tokens [8*(lane/8), +8) of the warp
-    const int l7 = lane & 7;
-    const int tb = lane >> 3;
-    const uint8_t* stage_rd = stage + l7 * kStagePitch + tb * 16;
     Tracer tr;
     tr.init(2);
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0, blk = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
@@ -406,10 +424,11 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
-      // first token this lane stores (8 consecutive tokens, 16 bytes) and whether it exists
-      const int w_st = tc.w0 + quarter * 32 + tb * 8;
-      const bool st_valid = w_st < p.n_walk && !(p.debug_skip & 1);  // n_walk % 8 == 0: all 8 or none
-      const long dst_tok = p.dst_base + tc.line * p.dst_line + w_st;
+      // the warp's 32 tokens start at walk index w_st; the store maps clip at the end of the walk
+      const int w_st = tc.w0 + quarter * 32;
+      const bool st_valid = w_st < p.n_walk;
+      const int dst_x = p.dst_x0 + w_st;
+      const int dst_y = p.dst_y0 + tc.line;
       for (int c = 0; c < kNumChunks; ++c) {
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
         ok = __all_sync(0xffffffffu, ok);
@@ -420,77 +439,67 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         sm100::tcgen05_fence_after_sync();
         if (ew == 0 && lane == 0) tr.ev(4);
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
-        // TMEM reads are software-pipelined: the load of the next 16 columns is in flight while the
-        // current 16 are processed (tcgen05.wait::ld is placed after the work on the other buffer).
         if (c < 4) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
           const int h = c >> 1;
-          constexpr int NS = C::CH / 2 / 16;   // 16-channel sub-groups this warp handles
-          const int colw = hh * (C::CH / 2);
+          constexpr int CW = C::CH / 4;   // channels of the chunk this warp handles
+          constexpr int NS = CW / 16;     // in 16-channel blocks
+          const int colw = part * CW;
           const float* bias_p0 = p.bias + c * D + colw;
           const bool has_mask = p.mask_kind != 0;
-          uint32_t pa[16], ga[16], pb[16], gb[16];
-          sm100::tmem_ld_32x32b_x16(trow + colw, pa);
-          sm100::tmem_ld_32x32b_x16(trow + C::CH + colw, ga);
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
+            uint32_t pv[16], gv[16];
+            sm100::tmem_ld_32x32b_x16(trow + colw + sg * 16, pv);
+            sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + sg * 16, gv);
+            // the block buffer written two stores ago must have been read by its TMA store; the
+            // first block after a gate chunk waits for that store too (it used both buffers)
+            if (lane == 0) {
+              if (c == 0 && sg == 0) sm100::tma_store_wait_read<0>();
+              else sm100::tma_store_wait_read<1>();
+            }
+            __syncwarp();
             sm100::tmem_ld_wait();
             if (ew == 0 && lane == 0) tr.ev(11);
-            if (sg + 1 < NS) {
-              if ((sg & 1) == 0) {
-                sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, pb);
-                sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + (sg + 1) * 16, gb);
-              } else {
-                sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, pa);
-                sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + (sg + 1) * 16, ga);
+            uint8_t* buf = stage + (blk & 1) * kBlockBytes;
+            gate_to_stage16_dispatch(p.has_bias, has_mask, pv, gv, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval,
+                                     stage_lane + (blk & 1) * kBlockBytes);
+            ++blk;
+            sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
+            __syncwarp();
+            if (ew == 0 && lane == 0) tr.ev(12);
+            if (lane == 0) {
+              if (st_valid && !(p.debug_skip & 1)) {
+                const int d = (c & 1) * C::CH + colw + sg * 16;  // first channel of the block inside the a (or b) half
+                sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], buf, dst_x, dst_y, tc.b, h * d_loc_n + (d & d_loc_mask));
               }
-            }
-            uint8_t* rows = stage_lane + (sg & 1) * 16 * kStagePitch;
-            if ((sg & 1) == 0) {
-              gate_to_stage16_dispatch(p.has_bias, has_mask, pa, ga, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval, rows);
-            } else {
-              gate_to_stage16_dispatch(p.has_bias, has_mask, pb, gb, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval, rows);
-              // 32 channels are staged: transpose out, 16 bytes (8 tokens of one channel) per lane and store
-              __syncwarp();
-              if (ew == 0 && lane == 0) tr.ev(12);
-              if (st_valid) {
-                const int d0 = (c & 1) * C::CH + colw + (sg - 1) * 16;  // first channel of the 32 inside the a (or b) half
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int d = d0 + 8 * j + l7;
-                  const long plane = (static_cast<long>(h) * d_loc_n + (d & d_loc_mask)) * p.batch + tc.b;
-                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[d >> p.d_loc_log2]) + plane * p.plane_elems + dst_tok;
-                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage_rd + j * 8 * kStagePitch);
-                }
-              }
-              __syncwarp();  // the stage is rewritten by the next pair of sub-groups
-              if (ew == 0 && lane == 0) tr.ev(13);
+              sm100::tma_store_commit();
             }
           }
         } else {
-          // output-gate chunk: sigmoid only, token-major local store
-          constexpr int NS = D / 2 / 16;
-          const int colw = hh * (D / 2);
+          // output-gate chunk: sigmoid only, token-major 32-token x 32-channel blocks to the local gate buffer
+          constexpr int GW = D / 4;
+          constexpr int NS = GW / 32;
+          const int colw = part * GW;
           const float* bias_g0 = p.bias + 4 * D + colw;
-          uint4* dst0 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gate_out) + srow * D + colw);
-          const bool do_store = valid && !(p.debug_skip & 2);
-          uint32_t ga[16], gb[16];
-          sm100::tmem_ld_32x32b_x16(trow + colw, ga);
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
+            uint32_t gv[32];
+            sm100::tmem_ld_32x32b_x32(trow + colw + sg * 32, gv);
+            if (lane == 0) sm100::tma_store_wait_read<0>();  // the gate block spans both a|b block buffers
+            __syncwarp();
             sm100::tmem_ld_wait();
-            if (sg + 1 < NS) {
-              if ((sg & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, gb);
-              else sm100::tmem_ld_32x32b_x16(trow + colw + (sg + 1) * 16, ga);
-            }
-            if (do_store) {
-              if ((sg & 1) == 0) {
-                if (p.has_bias) gate16_to_global<true>(ga, bias_g0 + sg * 16, dst0 + sg * 2);
-                else gate16_to_global<false>(ga, bias_g0 + sg * 16, dst0 + sg * 2);
-              } else {
-                if (p.has_bias) gate16_to_global<true>(gb, bias_g0 + sg * 16, dst0 + sg * 2);
-                else gate16_to_global<false>(gb, bias_g0 + sg * 16, dst0 + sg * 2);
+            if (p.has_bias) gate32_to_stage<true>(gv, bias_g0 + sg * 32, stage, lane);
+            else gate32_to_stage<false>(gv, bias_g0 + sg * 32, stage, lane);
+            sm100::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (st_valid && !(p.debug_skip & 2)) {
+                const int cw = p.gate_walk_dim == 1 ? w_st : tc.line;
+                const int cl = p.gate_walk_dim == 1 ? tc.line : w_st;
+                sm100::tma_store_4d(&om.gate, stage, colw + sg * 32, cw, cl, tc.b);
               }
+              sm100::tma_store_commit();
             }
           }
         }
@@ -504,6 +513,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const GatedProjArgs p
         }
       }
     }
+    if (lane == 0) sm100::tma_store_wait_all<0>();  // every bulk store of this warp has been performed
+    __syncwarp();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -546,7 +557,8 @@ int gated_proj_smem_bytes(int D) {
 }
 
 template <int D>
-static cudaError_t launch_t(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream) {
+static cudaError_t launch_t(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
+                            cudaStream_t stream) {
   cudaError_t e =
       cudaFuncSetAttribute(gated_proj_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
   if (e != cudaSuccess) return e;
@@ -554,13 +566,14 @@ static cudaError_t launch_t(const CUtensorMap& tmW, const GatedProjArgs& args, i
   const long total = static_cast<long>(args.batch) * args.n_lines * tiles_per_line;
   if (total <= 0) return cudaSuccess;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
-  gated_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, args);
+  gated_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, maps, args);
   return cudaGetLastError();
 }
 
-cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream) {
-  if (args.D == 128) return launch_t<128>(tmW, args, num_sms, stream);
-  if (args.D == 256) return launch_t<256>(tmW, args, num_sms, stream);
+cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
+                              cudaStream_t stream) {
+  if (args.D == 128) return launch_t<128>(tmW, maps, args, num_sms, stream);
+  if (args.D == 256) return launch_t<256>(tmW, maps, args, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

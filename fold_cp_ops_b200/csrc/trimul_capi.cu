@@ -44,9 +44,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// bf16 tensor, innermost dim contiguous, 128-byte swizzle, zero fill out of bounds.
+// bf16 tensor, innermost dim contiguous, 128-byte swizzle unless told otherwise, zero fill out of bounds.
 int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-              const uint32_t* box) {
+              const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(TRIMUL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[5];
@@ -60,7 +60,7 @@ int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims
     if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
   }
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim,
-                  gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(TRIMUL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return TRIMUL_OK;
@@ -354,10 +354,45 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   a.d_loc_log2 = d.d_loc_log2;
   a.plane_elems = plan.plane_elems;
   a.gate_out = gate_out;
-  a.debug_skip = debug_skip_bits() & 7;
+  if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d: a plane must hold fewer than 2^31 tokens", geom->n);
+  trimul::GatedOutMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  {
+    // Store maps.  a|b: every owner's operand buffer as (x, y, batch, 2*D_loc planes); x is clipped
+    // at the end of this rank's walk so a ragged tile cannot reach a neighbour's tokens.
+    const uint64_t n = static_cast<uint64_t>(geom->n);
+    const bool flat = plan.dst_line == 0;  // whole block contiguous: one line, x runs over the plane
+    a.dst_x0 = static_cast<int>(flat ? plan.dst_base : plan.dst_base % plan.dst_line);
+    a.dst_y0 = static_cast<int>(flat ? 0 : plan.dst_base / plan.dst_line);
+    const uint64_t dims[4] = {static_cast<uint64_t>(a.dst_x0) + static_cast<uint64_t>(plan.n_walk), flat ? 1 : n,
+                              static_cast<uint64_t>(geom->batch), static_cast<uint64_t>(2 * d.d_loc)};
+    const uint64_t strides[3] = {flat ? n * n * 2 : n * 2, n * n * 2, n * n * 2 * geom->batch};
+    const uint32_t box[4] = {32, 1, 1, 16};
+    for (int s = 0; s < d.cp; ++s) {
+      rc = make_tmap(&maps.ab[s], ab_peers[s], 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc != TRIMUL_OK) return rc;
+    }
+    // gate: local (rows, D) buffer as (D, walk | line, line | walk, batch), the smaller row stride first
+    const uint64_t row_b = static_cast<uint64_t>(D) * 2;
+    const uint64_t line_stride = (plan.n_lines > 1 ? static_cast<uint64_t>(plan.line_rows) : static_cast<uint64_t>(plan.batch_rows)) * row_b;
+    const uint64_t walk_stride = static_cast<uint64_t>(plan.walk_rows) * row_b;
+    const uint64_t batch_stride = static_cast<uint64_t>(plan.batch_rows) * row_b;
+    const bool walk_first = walk_stride <= line_stride;
+    a.gate_walk_dim = walk_first ? 1 : 2;
+    const uint64_t gdims[4] = {static_cast<uint64_t>(D),
+                               static_cast<uint64_t>(walk_first ? plan.n_walk : plan.n_lines),
+                               static_cast<uint64_t>(walk_first ? plan.n_lines : plan.n_walk),
+                               static_cast<uint64_t>(geom->batch)};
+    const uint64_t gstr[3] = {walk_first ? walk_stride : line_stride, walk_first ? line_stride : walk_stride, batch_stride};
+    const uint32_t gbox[4] = {32, walk_first ? 32u : 1u, walk_first ? 1u : 32u, 1};
+    rc = make_tmap(&maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 3) << 3;  // bits 10-11: weight-stream probes
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_gated_proj(tmW, a, num_sms_current(), stream);
+  cudaError_t e = trimul::launch_gated_proj(tmW, maps, a, num_sms_current(), stream);
   if (e != cudaSuccess) return cuda_fail(e, "ln_gated_proj launch");
   return TRIMUL_OK;
 }

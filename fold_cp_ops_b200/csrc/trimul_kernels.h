@@ -39,14 +39,26 @@ struct GatedProjArgs {
   long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane
+  int dst_x0, dst_y0;    // the same origin as tensor-map coordinates: dst_base = dst_y0 * dst_line + dst_x0
+  int gate_walk_dim;     // which coordinate of the gate map the walk index is (1 or 2; the line index is the other)
   void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
   int debug_skip;        // profiling aid (TRIMUL_DEBUG_SKIP): bit0 skip a|b stores, bit1 skip gate stores, bit2 skip x loads
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
 
+// Store-side tensor maps of the projection kernel.  ab[s]: rank s's operand buffer as
+// (x, y, batch, 2*D_loc planes), box 32 tokens x 16 planes, no swizzle; dim 0 is clipped at the end of
+// this rank's walk so ragged tiles never touch a neighbour's tokens.  gate: the local gate buffer
+// as (D, walk | line, line | walk, batch), box 32 channels x 32 tokens, 64-byte swizzle.
+struct GatedOutMaps {
+  CUtensorMap ab[kMaxPeers];
+  CUtensorMap gate;
+};
+
 int gated_proj_smem_bytes(int D);
-cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedProjArgs& args, int num_sms, cudaStream_t stream);
+cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
+                              cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // K_B  per-channel N x N x N contraction, back reshard fused in the store
