@@ -468,12 +468,33 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
             __syncwarp();
             if (ew == 0 && lane == 0) tr.ev(12);
-            if (lane == 0) {
-              if (st_valid && !(p.debug_skip & 1)) {
-                const int d = (c & 1) * C::CH + colw + sg * 16;  // first channel of the block inside the a (or b) half
-                sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], buf, dst_x, dst_y, tc.b, h * d_loc_n + (d & d_loc_mask));
+            const int d = (c & 1) * C::CH + colw + sg * 16;  // first channel of the block inside the a (or b) half
+            const int owner = d >> p.d_loc_log2;
+            if (owner == p.self_rank || p.self_rank == -2) {
+              // this GPU owns the channels: one bulk store of the whole block
+              if (lane == 0) {
+                if (st_valid && !(p.debug_skip & 1)) {
+                  sm100::tma_store_4d(&om.ab[owner], buf, dst_x, dst_y, tc.b, h * d_loc_n + (d & d_loc_mask));
+                }
+                sm100::tma_store_commit();
               }
-              sm100::tma_store_commit();
+            } else {
+              // a peer owns them: 16-byte stores (8 tokens of one channel per lane, the 64-byte row of a
+              // channel per 4 lanes) straight into its plane.  Plain stores queue in the memory system,
+              // so a busy NVLink does not hold the block buffer the way a bulk store does.
+              const int tb = lane & 3;
+              const int w8 = w_st + tb * 8;
+              if (w8 < p.n_walk && !(p.debug_skip & 1)) {  // n_walk % 8 == 0: all 8 tokens or none
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const int row = 8 * j + (lane >> 2);
+                  const long plane = (static_cast<long>(h) * d_loc_n + ((d + row) & d_loc_mask)) * p.batch + tc.b;
+                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[owner]) + plane * p.plane_elems + p.dst_base +
+                                       tc.line * p.dst_line + w8;
+                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(buf + row * kStagePitch + tb * 16);
+                }
+              }
+              if (lane == 0) sm100::tma_store_commit();  // keeps the two-deep buffer accounting uniform
             }
           }
         } else {

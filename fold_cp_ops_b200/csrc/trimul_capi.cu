@@ -353,6 +353,8 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   }
   a.d_loc_log2 = d.d_loc_log2;
   a.plane_elems = plan.plane_elems;
+  a.self_rank = (debug_skip_bits() >> 12) & 1 ? -1 : geom->rank;  // bit 12: every a|b block takes the plain-store path
+  if ((debug_skip_bits() >> 13) & 1) a.self_rank = -2;              // bit 13: every a|b block takes the TMA path
   a.gate_out = gate_out;
   if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
     return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d: a plane must hold fewer than 2^31 tokens", geom->n);

@@ -39,6 +39,7 @@ struct GatedProjArgs {
   long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane
+  int self_rank;         // index of this rank in ab.ptr: blocks it owns go out as TMA stores, the others as plain stores
   int dst_x0, dst_y0;    // the same origin as tensor-map coordinates: dst_base = dst_y0 * dst_line + dst_x0
   int gate_walk_dim;     // which coordinate of the gate map the walk index is (1 or 2; the line index is the other)
   void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
