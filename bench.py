@@ -58,8 +58,14 @@ def measured_peaks():
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
+KB_DRAM_BYTES_PER_PLANE_ELEMENT = 5.907
+
+
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 100 ms from warm-up to the end of the timed
+    work.  The report prefers the samples that fall inside the timed steps; when the timed region is too
+    short to hold three samples it widens to everything sampled under load (warm-up, timed steps,
+    per-stage passes) and says so in `window`."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -68,31 +74,35 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines = []
+        self.lines = []   # (host time of receipt, csv line)
+        self.t_load = self.t0 = self.t1 = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
+        self.t_load = time.time()
         return self
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=3)
-            except Exception:
-                self.proc.kill()
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    def _summary(self, lo, hi):
         sm, smax, reasons = [], [], set()
-        for ln in self.lines:
+        for ts, ln in self.lines:
+            if ts < lo or ts > hi:
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -107,6 +117,23 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+    def stop(self):
+        t_stop = time.time()
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+        if self.t0 is not None and self.t1 is not None:
+            r = self._summary(self.t0, self.t1 + 0.05)
+            if r["samples"] >= 3:
+                r["window"] = "timed steps"
+                return r
+        r = self._summary(self.t_load + 0.3, t_stop)
+        r["window"] = "warm-up + timed steps + per-stage passes (timed region shorter than three 100 ms samples)"
+        return r
 
 
 def make_layer_weights(D, seed, device):
@@ -243,20 +270,23 @@ def run_ours(args):
         out_host.copy_(ol, non_blocking=True)
 
     n_warm = args.warmup if args.kernels_only else max(3, args.warmup)
+    sampler = ClockSampler(dev.index).start() if rank == 0 else None
     for _ in range(n_warm):
         out = step_resident()
     barrier()
     # ---- value: inputs resident in HBM ---------------------------------------------------------
-    sampler = ClockSampler(dev.index).start() if rank == 0 else None
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     barrier()
+    if sampler:
+        sampler.mark_begin()
     ev[0].record()
     for _ in range(args.steps):
         out = step_resident()
     ev[1].record()
     barrier()
+    if sampler:
+        sampler.mark_end()
     ms = ev[0].elapsed_time(ev[1]) / args.steps
-    clocks = sampler.stop() if sampler else None
     # ---- per-stage timing of the dominant kernel (live, CUDA events on the launching stream) ----
     stage_ms = None
     eng = None
@@ -277,6 +307,7 @@ def run_ours(args):
                     acc.setdefault(k, []).append(v)
         eng.stage_log = False
         stage_ms = {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
+    clocks = sampler.stop() if sampler else None
     # ---- e2e: pinned host -> device, forward, device -> pinned host, every step -----------------
     ms_e2e = float("nan")
     if not args.kernels_only:
@@ -310,7 +341,12 @@ def run_ours(args):
         ach = fl_b / (t_b * 1e-3) / 1e12 if t_b > 0 else None
         peak = peaks["bf16_tflops_sustained"]
         roof = {"bound": "tensor", "kernel": "tri_contract_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                "frac": (ach / peak) if ach else None, "traffic": None,
+                "frac": (ach / peak) if ach else None,
+                # DRAM bytes per launch: ncu measured 5.907 B per plane element (read 4.000 + write 1.907) on
+                # profile_n1024_d256 (profiles/tri_contract_kernel_n1024_d256.md); first-touch traffic only, so it
+                # scales with planes * N^2
+                "traffic": KB_DRAM_BYTES_PER_PLANE_ELEMENT * B * (D / cp) * N * N,
+                "traffic_unit": "bytes per launch (ncu capture at N=1024 scaled by planes*N^2)",
                 "peak_source": f"{peaks['source']} (sustained: the kernel runs inside a long step)",
                 "frac_of_burst_peak": (ach / peaks["bf16_tflops"]) if ach else None,
                 "stage_ms": {"ln_gated_proj": t_a, "tri_contract": t_b, "ln_out_proj": t_c}}
