@@ -11,14 +11,15 @@
 // Persistent CTA, 128-token tiles.  Eight LayerNorm warps pull token rows from HBM into
 // registers, normalise them there (two-pass fp32 statistics), and write the bf16 operand tile into
 // shared memory in the K-major 128-byte-swizzle layout once the tensor core has released it;
-// weights stream through a four-stage TMA ring (they live in L2); one thread issues tcgen05.mma
-// for five N=D column chunks per tile into two TMEM accumulators; sixteen epilogue warps (four per
-// TMEM lane quarter) apply bias / gate / mask, write 16-channel x 32-token blocks channel-major
-// into a small per-warp shared-memory stage, and hand each block to a TMA store into the
+// weights stream through a TMA ring (they live in L2); one thread issues tcgen05.mma for five
+// N=D column chunks per tile into two TMEM accumulators; sixteen epilogue warps (four per TMEM
+// lane quarter) apply bias / gate / mask and write bf16 into a CTA-wide staging tile
+// [channel][128 tokens] (double-buffered); when all sixteen have arrived, one forwarding thread
+// sends the tile as TMA stores of 16 channels x 128 tokens -- 256-byte rows -- into the
 // channel-major operand plane of the rank that owns the channels (front all-to-all fused in the
-// store; at cp=1 that rank is this GPU).  The output gate goes out the same way, token-major.
-// No epilogue thread issues a global store: scattered 16-byte stores from 512 threads cost this
-// kernel 40 % of its time, bulk stores of whole blocks are asynchronous and full-sector.
+// store; at cp=1 that rank is this GPU).  The output gate leaves the same way, token-major.
+// No thread issues a global store: per-thread 16-byte stores cost this kernel 40 % of its time,
+// and rows shorter than 128 bytes reach half of the HBM / NVLink write rate.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -36,9 +37,8 @@ constexpr int kEpiWarp0 = 4;
 constexpr int kLnWarp0 = kEpiWarp0 + kEpiWarps;
 constexpr int kThreads = (kLnWarp0 + kLnWarps) * 32;
 constexpr int kNumChunks = 5;            // a_lo, a_hi, b_lo, b_hi, gate
-constexpr int kStagePitch = 64;          // bytes per channel row of an a|b block: 32 tokens, dense (TMA box layout)
-constexpr int kBlockBytes = 16 * kStagePitch;   // one a|b block: 16 channels x 32 tokens
-constexpr int kStageBytes = 2 * kBlockBytes;    // per warp: two a|b blocks, or one 32-token x 32-channel gate block
+constexpr int kRowPitch = BM * 2;        // bytes per channel row of the a|b staging tile (128 tokens)
+constexpr int kFwdWarp = 3;              // control warp whose lane 0 forwards staged tiles
 
 template <int D>
 struct Cfg {
@@ -47,10 +47,12 @@ struct Cfg {
   static constexpr int kABytes = BM * D * 2;    // one operand tile
   static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
   static constexpr int kWStageBytes = D * 128;  // D weight rows x 64 k
-  static constexpr int kWStages = 4;
+  static constexpr int kWStages = (D == 256) ? 3 : 4;
   static constexpr int kABufs = (D == 256) ? 1 : 2;
   static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
-  static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes;
+  static constexpr int kStageBuf = CH * kRowPitch;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or half of the gate tile
+  static constexpr int kGateBoxBytes = BM * 128;     // gate box: 128 tokens x 64 channels, 128-byte swizzle
+  static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes + 2 * kStageBuf;
 };
 
 template <int D>
@@ -61,10 +63,11 @@ struct SmemCtl {
   uint64_t x_empty[2];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t st_full[2];   // staging buffer written by all sixteen epilogue warps
+  uint64_t st_free[2];   // ... and read completely by the forwarder's bulk stores
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kWStages];
-  alignas(1024) uint8_t stage[kEpiWarps][kStageBytes];  // one transpose stage per epilogue warp
 };
 
 template <int D>
@@ -97,7 +100,8 @@ __device__ __forceinline__ float tanh_approx(float x) {
 }
 
 // Sixteen channels of a gated chunk for this thread's token: pv = p/2 and gv = g/2 accumulators.
-// The bf16 results go to the warp's transpose stage as stage[channel][token-in-warp].
+// The bf16 results go to the staging tile as tile[channel][token] (256-byte rows, the dense layout
+// of a (128 token, 16 channel) TMA box); the 2-byte stores of a warp are conflict-free.
 template <bool HAS_BIAS, bool HAS_MASK>
 __device__ __forceinline__ void gate_to_stage16(const uint32_t (&pv)[16], const uint32_t (&gv)[16], const float* bias_p,
                                                 const float* bias_g, float mval, uint8_t* stage_rows) {
@@ -111,7 +115,7 @@ __device__ __forceinline__ void gate_to_stage16(const uint32_t (&pv)[16], const 
     }
     float val = fmaf(pr, tanh_approx(ga), pr);
     if (HAS_MASK) val *= mval;
-    *reinterpret_cast<__nv_bfloat16*>(stage_rows + e * kStagePitch) = __float2bfloat16_rn(val);
+    *reinterpret_cast<__nv_bfloat16*>(stage_rows + e * kRowPitch) = __float2bfloat16_rn(val);
   }
 }
 
@@ -127,15 +131,16 @@ __device__ __forceinline__ void gate_to_stage16_dispatch(int has_bias, bool has_
   }
 }
 
-// Thirty-two output-gate channels of this thread's token: sigmoid, bf16, written as the token's
-// 64-byte row of the warp's gate block in the 64-byte-swizzle layout the TMA store expects
-// (16-byte slot index ^ ((row / 2) % 4)); conflict-free for 16-byte stores.
+// Sixteen output-gate channels of this thread's token: sigmoid, bf16, written as two 16-byte slots
+// (slot0, slot0 + 1) of the token's 128-byte row of a (128 token x 64 channel) gate box, in the
+// 128-byte-swizzle layout the TMA store expects (slot ^ (row % 8)); conflict-free.
 template <bool HAS_BIAS>
-__device__ __forceinline__ void gate32_to_stage(const uint32_t (&gv)[32], const float* bias_g, uint8_t* stage, int row) {
-  uint8_t* row_ptr = stage + row * 64;
-  const int sw = (row >> 1) & 3;
+__device__ __forceinline__ void gate16_to_stage(const uint32_t (&gv)[16], const float* bias_g, uint8_t* box, int row,
+                                                int slot0) {
+  uint8_t* row_ptr = box + row * 128;
+  const int sw = row & 7;
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
+  for (int q = 0; q < 2; ++q) {
     float s[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -148,7 +153,7 @@ __device__ __forceinline__ void gate32_to_stage(const uint32_t (&gv)[32], const 
     pk.y = sm100::pack_bf16x2(s[2], s[3]);
     pk.z = sm100::pack_bf16x2(s[4], s[5]);
     pk.w = sm100::pack_bf16x2(s[6], s[7]);
-    *reinterpret_cast<uint4*>(row_ptr + ((q ^ sw) << 4)) = pk;
+    *reinterpret_cast<uint4*>(row_ptr + (((slot0 + q) ^ sw) << 4)) = pk;
   }
 }
 
@@ -184,6 +189,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = tiles;                              // kABufs x kABytes
   uint8_t* w_tiles = tiles + C::kABufs * C::kABytes;     // kWStages x kWStageBytes
+  uint8_t* st_tiles = w_tiles + C::kWStages * C::kWStageBytes;  // 2 x kStageBuf
   SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -203,6 +209,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sm100::mbar_init(&ctl->x_empty[a], 1);     // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_full[a], 1);   // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_empty[a], kEpiWarps);  // one arrive per epilogue warp
+      sm100::mbar_init(&ctl->st_full[a], kEpiWarps);     // one arrive per epilogue warp
+      sm100::mbar_init(&ctl->st_free[a], 1);             // the forwarder
     }
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
@@ -306,6 +314,54 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           buf_phase ^= 1;
         }
       }
+    } else if (warp == kFwdWarp && lane == 0) {
+      // ---------------------------------------------------------- forwarder (TMA stores of staged tiles)
+      // Six buffer uses per tile: four a|b chunks (one buffer each) and the gate tile (both buffers).
+      const int d_loc_mask = (1 << p.d_loc_log2) - 1;
+      const int d_loc_n = 1 << p.d_loc_log2;
+      uint32_t use = 0;  // running count of buffer uses; buffer = use & 1, phase = (use >> 1) & 1
+      bool ok = true;
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
+        const int dst_x = p.dst_x0 + tc.w0;
+        const int dst_y = p.dst_y0 + tc.line;
+        for (int c = 0; c < kNumChunks && ok; ++c) {
+          const int n_use = (c < 4) ? 1 : 2;
+          for (int u = 0; u < n_use; ++u) {
+            const uint32_t b = (use + u) & 1, ph = ((use + u) >> 1) & 1;
+            if (!sm100::mbar_wait(&ctl->st_full[b], ph, abort_flag, tmo)) {
+              report_timeout(p.status, kKernelGatedProj, 4, c);
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          if (c < 4) {
+            const uint8_t* src = st_tiles + (use & 1) * C::kStageBuf;
+            const int h = c >> 1;
+            if (!(p.debug_skip & 1)) {
+#pragma unroll 1
+              for (int k = 0; k < C::CH / 16; ++k) {
+                const int d = (c & 1) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
+                sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], src + k * 16 * kRowPitch, dst_x, dst_y, tc.b,
+                                    h * d_loc_n + (d & d_loc_mask));
+              }
+            }
+          } else if (!(p.debug_skip & 2)) {
+            const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
+            const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
+#pragma unroll 1
+            for (int jb = 0; jb < D / 64; ++jb) {
+              sm100::tma_store_4d(&om.gate, st_tiles + jb * C::kGateBoxBytes, jb * 64, cw, cl, tc.b);
+            }
+          }
+          sm100::tma_store_commit();
+          sm100::tma_store_wait_read<0>();  // the bulk stores have read the staging buffer(s)
+          for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_free[(use + u) & 1]);
+          use += n_use;
+        }
+      }
+      sm100::tma_store_wait_all<0>();  // every bulk store has been performed before the CTA retires
     }
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
@@ -400,14 +456,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int ew = warp - kEpiWarp0;
     const int quarter = warp & 3;   // TMEM lane quarter this warp may read
     const int part = ew >> 2;       // which quarter of the chunk's columns
-    const int r = quarter * 32 + lane;
-    const int d_loc_mask = (1 << p.d_loc_log2) - 1;
-    const int d_loc_n = 1 << p.d_loc_log2;
-    uint8_t* stage = ctl->stage[ew];
-    uint8_t* stage_lane = stage + lane * 2;
+    const int r = quarter * 32 + lane;  // token row of this thread inside the tile
     Tracer tr;
     tr.init(2);
-    uint32_t acc = 0, acc_phase = 0, blk = 0;
+    uint32_t acc = 0, acc_phase = 0, use = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
@@ -424,13 +476,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
-      // the warp's 32 tokens start at walk index w_st; the store maps clip at the end of the walk
-      const int w_st = tc.w0 + quarter * 32;
-      const bool st_valid = w_st < p.n_walk;
-      const int dst_x = p.dst_x0 + w_st;
-      const int dst_y = p.dst_y0 + tc.line;
       for (int c = 0; c < kNumChunks; ++c) {
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
+        // the staging buffer(s) of this chunk must have been forwarded (two uses ago)
+        const int n_use = (c < 4) ? 1 : 2;
+        for (int u = 0; u < n_use; ++u) {
+          const uint32_t b = (use + u) & 1, ph = ((use + u) >> 1) & 1;
+          ok = ok && sm100::mbar_wait(&ctl->st_free[b], ph ^ 1, abort_flag, tmo);
+        }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           report_timeout(p.status, kKernelGatedProj, 2, c);
@@ -441,92 +494,49 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
         if (c < 4) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
-          const int h = c >> 1;
           constexpr int CW = C::CH / 4;   // channels of the chunk this warp handles
-          constexpr int NS = CW / 16;     // in 16-channel blocks
+          constexpr int NS = CW / 16;     // in 16-channel sub-groups
           const int colw = part * CW;
           const float* bias_p0 = p.bias + c * D + colw;
           const bool has_mask = p.mask_kind != 0;
+          uint8_t* rows = st_tiles + (use & 1) * C::kStageBuf + colw * kRowPitch + r * 2;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
             uint32_t pv[16], gv[16];
             sm100::tmem_ld_32x32b_x16(trow + colw + sg * 16, pv);
             sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + sg * 16, gv);
-            // the block buffer written two stores ago must have been read by its TMA store; the
-            // first block after a gate chunk waits for that store too (it used both buffers)
-            if (lane == 0) {
-              if (c == 0 && sg == 0) sm100::tma_store_wait_read<0>();
-              else sm100::tma_store_wait_read<1>();
-            }
-            __syncwarp();
             sm100::tmem_ld_wait();
             if (ew == 0 && lane == 0) tr.ev(11);
-            uint8_t* buf = stage + (blk & 1) * kBlockBytes;
             gate_to_stage16_dispatch(p.has_bias, has_mask, pv, gv, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval,
-                                     stage_lane + (blk & 1) * kBlockBytes);
-            ++blk;
-            sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
-            __syncwarp();
+                                     rows + sg * 16 * kRowPitch);
             if (ew == 0 && lane == 0) tr.ev(12);
-            const int d = (c & 1) * C::CH + colw + sg * 16;  // first channel of the block inside the a (or b) half
-            const int owner = d >> p.d_loc_log2;
-            if (owner == p.self_rank || p.self_rank == -2) {
-              // this GPU owns the channels: one bulk store of the whole block
-              if (lane == 0) {
-                if (st_valid && !(p.debug_skip & 1)) {
-                  sm100::tma_store_4d(&om.ab[owner], buf, dst_x, dst_y, tc.b, h * d_loc_n + (d & d_loc_mask));
-                }
-                sm100::tma_store_commit();
-              }
-            } else {
-              // a peer owns them: 16-byte stores (8 tokens of one channel per lane, the 64-byte row of a
-              // channel per 4 lanes) straight into its plane.  Plain stores queue in the memory system,
-              // so a busy NVLink does not hold the block buffer the way a bulk store does.
-              const int tb = lane & 3;
-              const int w8 = w_st + tb * 8;
-              if (w8 < p.n_walk && !(p.debug_skip & 1)) {  // n_walk % 8 == 0: all 8 tokens or none
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                  const int row = 8 * j + (lane >> 2);
-                  const long plane = (static_cast<long>(h) * d_loc_n + ((d + row) & d_loc_mask)) * p.batch + tc.b;
-                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ab.ptr[owner]) + plane * p.plane_elems + p.dst_base +
-                                       tc.line * p.dst_line + w8;
-                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(buf + row * kStagePitch + tb * 16);
-                }
-              }
-              if (lane == 0) sm100::tma_store_commit();  // keeps the two-deep buffer accounting uniform
-            }
           }
         } else {
-          // output-gate chunk: sigmoid only, token-major 32-token x 32-channel blocks to the local gate buffer
+          // output-gate chunk: sigmoid only, token-major, into (128 token x 64 channel) boxes
           constexpr int GW = D / 4;
-          constexpr int NS = GW / 32;
+          constexpr int NS = GW / 16;
           const int colw = part * GW;
           const float* bias_g0 = p.bias + 4 * D + colw;
+          uint8_t* box = st_tiles + (colw >> 6) * C::kGateBoxBytes;
+          const int slot_base = (colw & 63) >> 3;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
-            uint32_t gv[32];
-            sm100::tmem_ld_32x32b_x32(trow + colw + sg * 32, gv);
-            if (lane == 0) sm100::tma_store_wait_read<0>();  // the gate block spans both a|b block buffers
-            __syncwarp();
+            uint32_t gv[16];
+            sm100::tmem_ld_32x32b_x16(trow + colw + sg * 16, gv);
             sm100::tmem_ld_wait();
-            if (p.has_bias) gate32_to_stage<true>(gv, bias_g0 + sg * 32, stage, lane);
-            else gate32_to_stage<false>(gv, bias_g0 + sg * 32, stage, lane);
-            sm100::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (st_valid && !(p.debug_skip & 2)) {
-                const int cw = p.gate_walk_dim == 1 ? w_st : tc.line;
-                const int cl = p.gate_walk_dim == 1 ? tc.line : w_st;
-                sm100::tma_store_4d(&om.gate, stage, colw + sg * 32, cw, cl, tc.b);
-              }
-              sm100::tma_store_commit();
-            }
+            if (p.has_bias) gate16_to_stage<true>(gv, bias_g0 + sg * 16, box, r, slot_base + sg * 2);
+            else gate16_to_stage<false>(gv, bias_g0 + sg * 16, box, r, slot_base + sg * 2);
           }
         }
+        // accumulator back to the tensor core, staged data over to the forwarder
         sm100::tcgen05_fence_before_sync();
+        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk stores
         __syncwarp();
-        if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+        if (lane == 0) {
+          sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+          for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_full[(use + u) & 1]);
+        }
+        use += n_use;
         if (ew == 0 && lane == 0) tr.ev(5);
         if (++acc == 2) {
           acc = 0;
@@ -534,8 +544,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     }
-    if (lane == 0) sm100::tma_store_wait_all<0>();  // every bulk store of this warp has been performed
-    __syncwarp();
   }
 
   // ------------------------------------------------------------------ teardown

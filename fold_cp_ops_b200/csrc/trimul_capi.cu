@@ -353,8 +353,6 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   }
   a.d_loc_log2 = d.d_loc_log2;
   a.plane_elems = plan.plane_elems;
-  a.self_rank = (debug_skip_bits() >> 12) & 1 ? -1 : geom->rank;  // bit 12: every a|b block takes the plain-store path
-  if ((debug_skip_bits() >> 13) & 1) a.self_rank = -2;              // bit 13: every a|b block takes the TMA path
   a.gate_out = gate_out;
   if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
     return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d: a plane must hold fewer than 2^31 tokens", geom->n);
@@ -370,7 +368,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
     const uint64_t dims[4] = {static_cast<uint64_t>(a.dst_x0) + static_cast<uint64_t>(plan.n_walk), flat ? 1 : n,
                               static_cast<uint64_t>(geom->batch), static_cast<uint64_t>(2 * d.d_loc)};
     const uint64_t strides[3] = {flat ? n * n * 2 : n * 2, n * n * 2, n * n * 2 * geom->batch};
-    const uint32_t box[4] = {32, 1, 1, 16};
+    const uint32_t box[4] = {128, 1, 1, 16};
     for (int s = 0; s < d.cp; ++s) {
       rc = make_tmap(&maps.ab[s], ab_peers[s], 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
       if (rc != TRIMUL_OK) return rc;
@@ -387,8 +385,8 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
                                static_cast<uint64_t>(walk_first ? plan.n_lines : plan.n_walk),
                                static_cast<uint64_t>(geom->batch)};
     const uint64_t gstr[3] = {walk_first ? walk_stride : line_stride, walk_first ? line_stride : walk_stride, batch_stride};
-    const uint32_t gbox[4] = {32, walk_first ? 32u : 1u, walk_first ? 1u : 32u, 1};
-    rc = make_tmap(&maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_64B);
+    const uint32_t gbox[4] = {64, walk_first ? 128u : 1u, walk_first ? 1u : 128u, 1};
+    rc = make_tmap(&maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TRIMUL_OK) return rc;
   }
   a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 3) << 3;  // bits 10-11: weight-stream probes

@@ -39,7 +39,6 @@ struct GatedProjArgs {
   long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane
-  int self_rank;         // index of this rank in ab.ptr: blocks it owns go out as TMA stores, the others as plain stores
   int dst_x0, dst_y0;    // the same origin as tensor-map coordinates: dst_base = dst_y0 * dst_line + dst_x0
   int gate_walk_dim;     // which coordinate of the gate map the walk index is (1 or 2; the line index is the other)
   void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
@@ -49,9 +48,9 @@ struct GatedProjArgs {
 };
 
 // Store-side tensor maps of the projection kernel.  ab[s]: rank s's operand buffer as
-// (x, y, batch, 2*D_loc planes), box 32 tokens x 16 planes, no swizzle; dim 0 is clipped at the end of
+// (x, y, batch, 2*D_loc planes), box 128 tokens x 16 planes, no swizzle; dim 0 is clipped at the end of
 // this rank's walk so ragged tiles never touch a neighbour's tokens.  gate: the local gate buffer
-// as (D, walk | line, line | walk, batch), box 32 channels x 32 tokens, 64-byte swizzle.
+// as (D, walk | line, line | walk, batch), box 64 channels x 128 tokens, 128-byte swizzle.
 struct GatedOutMaps {
   CUtensorMap ab[kMaxPeers];
   CUtensorMap gate;
