@@ -62,35 +62,55 @@ KB_DRAM_BYTES_PER_PLANE_ELEMENT = 5.907
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 100 ms from warm-up to the end of the timed
-    work.  The report prefers the samples that fall inside the timed steps; when the timed region is too
-    short to hold three samples it widens to everything sampled under load (warm-up, timed steps,
-    per-stage passes) and says so in `window`."""
+    """Samples SM clock and clock-event (throttle) reasons every 50 ms through NVML (read-only) from
+    warm-up to the end of the timed work.  The report prefers the samples that fall inside the timed
+    steps; when the timed region is too short to hold three samples it widens to everything sampled
+    under load (warm-up, timed steps, per-stage passes) and says so in `window`."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []   # (host time of receipt, csv line)
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.samples = []   # (host time, sm MHz, reason bitmask)
+        self.max_mhz = None
         self.t_load = self.t0 = self.t1 = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.error = None
+
+    def _handle(self, nv):
+        try:
+            pr = torch.cuda.get_device_properties(self.device)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            return nv.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return nv.nvmlDeviceGetHandleByIndex(self.device.index or 0)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-        except Exception:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            h = self._handle(nv)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+
+            def pump():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append((time.time(), float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                             int(reasons_fn(h))))
+                    except Exception as e:  # keep what was sampled
+                        self.error = repr(e)
+                        return
+                    self._stop.wait(0.05)
+
+            self._thread = threading.Thread(target=pump, daemon=True)
+            self._thread.start()
+        except Exception as e:
+            self.error = repr(e)
         self.t_load = time.time()
         return self
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
 
     def mark_begin(self):
         self.t0 = time.time()
@@ -99,40 +119,30 @@ class ClockSampler:
         self.t1 = time.time()
 
     def _summary(self, lo, hi):
-        sm, smax, reasons = [], [], set()
-        for ts, ln in self.lines:
-            if ts < lo or ts > hi:
-                continue
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
+        sm, bits = [], 0
+        for ts, mhz, r in self.samples:
+            if lo <= ts <= hi:
+                sm.append(mhz)
+                bits |= r
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz,
+               "reasons": [name for bit, name in self.REASONS if bits & bit], "samples": len(sm)}
+        if self.error:
+            out["error"] = self.error
+        return out
 
     def stop(self):
         t_stop = time.time()
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=3)
-            except Exception:
-                self.proc.kill()
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
         if self.t0 is not None and self.t1 is not None:
-            r = self._summary(self.t0, self.t1 + 0.05)
+            r = self._summary(self.t0, self.t1)
             if r["samples"] >= 3:
                 r["window"] = "timed steps"
                 return r
-        r = self._summary(self.t_load + 0.3, t_stop)
-        r["window"] = "warm-up + timed steps + per-stage passes (timed region shorter than three 100 ms samples)"
+        r = self._summary(self.t_load + 0.2, t_stop)
+        r["window"] = "warm-up + timed steps + per-stage passes (timed region shorter than three 50 ms samples)"
         return r
 
 
@@ -270,7 +280,7 @@ def run_ours(args):
         out_host.copy_(ol, non_blocking=True)
 
     n_warm = args.warmup if args.kernels_only else max(3, args.warmup)
-    sampler = ClockSampler(dev.index).start() if rank == 0 else None
+    sampler = ClockSampler(dev).start() if rank == 0 else None
     for _ in range(n_warm):
         out = step_resident()
     barrier()
