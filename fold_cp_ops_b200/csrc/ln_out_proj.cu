@@ -10,16 +10,18 @@
 // The LayerNorm is folded algebraically so the channel-major tile never has to be transposed or
 // rewritten:   LN(x) W^T + b  =  rstd * ( x (gamma .* W)^T  -  mean * c )  +  d ,
 //     c[n] = sum_k bf16(gamma_k W[n,k]),   d[n] = sum_k beta_k W[n,k] + b[n]        (packed once).
-// The GEMM is issued transposed -- acc[n][m] = sum_k W'[n][k] tri[k][m] -- so that TMEM lanes are
-// output CHANNELS and columns are tokens: an epilogue warp then touches 32 consecutive channels of
-// one token per instruction (64 contiguous bytes of the token-major gate / out rows) instead of 32
-// different rows.  The raw tile is the B operand exactly as it lies in memory: TMA brings
-// (64 channels x 64 tokens) boxes with the 128-byte swizzle along TOKENS, and the tensor core
-// reads them through an MN-major (token-major) shared-memory descriptor.  Eight statistics warps read the same staged boxes and
-// reduce per-token mean / M2 (two-pass per 16 channels, Chan-merged), so the tile is fetched from
-// HBM exactly once, asynchronously, through a 5..8 stage ring.  gamma .* W stays resident in
-// shared memory.  Eight epilogue warps (one channel per lane) apply
-// rstd[m] * acc + (-mean[m]*rstd[m]) * c[n] + d[n], multiply by the gate and store token-major.
+// The raw tile is the A operand exactly as it lies in memory: TMA brings (64 channels x 64
+// tokens) boxes with the 128-byte swizzle along TOKENS and the tensor core reads them through an
+// MN-major shared-memory descriptor; the folded weights stream from L2 beside it (one ring stage
+// = one 64-channel K block of both operands).  Eight statistics warps read the same staged boxes
+// and reduce per-token mean / M2 (two-pass per 16 channels, Chan-merged), so the tile is fetched
+// from HBM exactly once.
+//
+// Every byte of global traffic moves as a TMA box with 128-byte rows: the gate arrives as
+// (128 token x 64 channel) boxes in a four-slot ring, eight epilogue warps (one token per thread)
+// combine it IN PLACE with  rstd[m] * acc + (-mean[m]*rstd[m]) * c[n] + d[n]  from TMEM, and a
+// forwarding thread sends each finished box to `out` and hands the slot back to the gate loader.
+// No thread issues a global load or store.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -28,37 +30,44 @@ namespace trimul {
 namespace {
 
 constexpr int BM = 128;
-// Five warpgroups: w0-3 control (w0 TMA producer, w1 MMA issuer, w2 TMEM alloc), w4-11 epilogue,
-// w12-19 statistics.
+// Five warpgroups: w0-3 control (w0 operand TMA, w1 MMA issue, w2 TMEM alloc + forwarder,
+// w3 gate TMA), w4-11 epilogue, w12-19 statistics.
 constexpr int kThreads = 640;
 constexpr int kEpiWarp0 = 4;
 constexpr int kStatWarp0 = 12;
-constexpr int kStageBytes = 2 * 64 * 128;  // two token blocks x 64 channels x 128 B
+constexpr int kTriBytes = 2 * 64 * 128;   // one K block of the tile: two token blocks x 64 channels x 128 B
+constexpr int kBoxBytes = BM * 128;       // gate / out box: 128 tokens x 64 channels
+constexpr int kBoxSlots = 4;
 
 template <int D>
 struct Cfg {
-  static constexpr int KB = D / 64;
-  static constexpr int kWBytes = D * D * 2;
-  static constexpr int kWBlockBytes = D * 128;
-  static constexpr int kStages = (D == 256) ? 5 : 8;
+  static constexpr int KB = D / 64;                // K blocks per tile
+  static constexpr int NBT = D / 64;               // gate / out boxes per tile
+  static constexpr int kWBytes = D * 128;          // one K block of the folded weights: D rows x 64 k
+  static constexpr int kStageBytes = kTriBytes + kWBytes;
+  static constexpr int kStages = (D == 256) ? 3 : 4;
   static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
-  static constexpr int kTileBytes = kWBytes + kStages * kStageBytes;
+  static constexpr int kTileBytes = kStages * kStageBytes + kBoxSlots * kBoxBytes;
 };
 
 template <int D>
 struct SmemCtl {
-  uint64_t w_full;
   uint64_t full[Cfg<D>::kStages];
   uint64_t empty[Cfg<D>::kStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t red_bar[2];
   uint64_t stats_ready[2];
+  uint64_t g_full[kBoxSlots];   // gate box landed (TMA transaction bytes)
+  uint64_t o_full[kBoxSlots];   // box overwritten with the result by the four warps that own it
+  uint64_t g_free[kBoxSlots];   // result read by its bulk store: the slot may be refilled
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kStages];
+  volatile uint32_t g_armed[kBoxSlots];
   alignas(16) float2 red[2][4][BM];   // [tile parity][channel subgroup][token] = (mean, M2) over D/4 channels
-  float2 stat[2][BM];     // [accumulator][token] = (rstd, -mean * rstd)
+  float2 stat[2][BM];                 // [accumulator][token] = (rstd, -mean * rstd)
+  float2 cd[D];                       // (c[n], d[n]) of the folded projection
 };
 
 template <int D>
@@ -66,30 +75,18 @@ constexpr int smem_bytes() {
   return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
-__device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
-  uint32_t v;
-  asm volatile("{\n\t.reg .b16 h;\n\tld.global.nc.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
 }  // namespace
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmT,
+                const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmO,
                 const OutProjArgs p) {
   using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* w_tiles = tiles;                 // KB blocks of (D rows x 64 k), K-major, resident
-  uint8_t* ring = tiles + C::kWBytes;       // kStages x [2 token blocks][64 channels][128 B]
+  uint8_t* ring = tiles;                                   // kStages x [tri K block | weight K block]
+  uint8_t* boxes = tiles + C::kStages * C::kStageBytes;    // kBoxSlots x kBoxBytes
   SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -98,7 +95,6 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const long my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
-    sm100::mbar_init(&ctl->w_full, 1);
     for (int s = 0; s < C::kStages; ++s) {
       sm100::mbar_init(&ctl->full[s], 1);
       sm100::mbar_init(&ctl->empty[s], 1 + 8);  // tcgen05.commit + one arrive per statistics warp
@@ -110,9 +106,16 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       sm100::mbar_init(&ctl->red_bar[a], 8);
       sm100::mbar_init(&ctl->stats_ready[a], 2);
     }
+    for (int s = 0; s < kBoxSlots; ++s) {
+      sm100::mbar_init(&ctl->g_full[s], 1);
+      sm100::mbar_init(&ctl->o_full[s], 4);
+      sm100::mbar_init(&ctl->g_free[s], 1);
+      ctl->g_armed[s] = 2;
+    }
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
   }
+  for (int n = threadIdx.x; n < D; n += kThreads) ctl->cd[n] = reinterpret_cast<const float2*>(p.cd)[n];
   if (warp == 2) {
     sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
     sm100::tmem_relinquish();
@@ -123,18 +126,12 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   const uint64_t tmo = p.timeout_ns;
-  bool w_armed = false;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ operand producer (tri from HBM, weights from L2)
     if (lane == 0 && my_tiles > 0) {
       sm100::tma_prefetch_desc(&tmW);
       sm100::tma_prefetch_desc(&tmT);
-      sm100::mbar_arrive_expect_tx(&ctl->w_full, C::kWBytes);
-      for (int kb = 0; kb < C::KB; ++kb) {
-        sm100::tma_load_2d(w_tiles + kb * C::kWBlockBytes, &tmW, &ctl->w_full, kb * 64, 0);
-      }
-      w_armed = true;
       PipeState ps{0, 0};
       bool ok = true;
       for (long it = 0; it < my_tiles && ok; ++it) {
@@ -145,12 +142,13 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             ok = false;
             break;
           }
-          uint8_t* st = ring + ps.stage * kStageBytes;
+          uint8_t* st = ring + ps.stage * C::kStageBytes;
           ctl->armed[ps.stage] = ps.phase;
-          sm100::mbar_arrive_expect_tx(&ctl->full[ps.stage], kStageBytes);
+          sm100::mbar_arrive_expect_tx(&ctl->full[ps.stage], C::kStageBytes);
           // (tokens, channels) boxes of 64 x 64; a block past the last token is zero-filled
           sm100::tma_load_2d(st, &tmT, &ctl->full[ps.stage], static_cast<int>(m0), kb * 64);
-          sm100::tma_load_2d(st + kStageBytes / 2, &tmT, &ctl->full[ps.stage], static_cast<int>(m0 + 64), kb * 64);
+          sm100::tma_load_2d(st + kTriBytes / 2, &tmT, &ctl->full[ps.stage], static_cast<int>(m0 + 64), kb * 64);
+          sm100::tma_load_2d(st + kTriBytes, &tmW, &ctl->full[ps.stage], kb * 64, 0);
           ps.advance(C::kStages);
         }
       }
@@ -158,17 +156,11 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
     if (lane == 0 && my_tiles > 0) {
-      // A: folded weights, K-major, one 128-channel M tile at a time; B: raw tile, token-major (MN-major)
-      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(128, BM) | (1u << 16);
-      constexpr int MT = D / 128;  // M tiles (output channels / 128)
+      // A: raw tile, token-major (MN-major); B: folded weights, K-major, all D output channels
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D) | (1u << 15);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0;
-      bool ok = sm100::mbar_wait(&ctl->w_full, 0, abort_flag, tmo);
-      if (!ok) report_timeout(p.status, kKernelOutProj, 1, -3);
-      const uint32_t w_addr = sm100::smem_u32(w_tiles);
-      // token blocks of 64 are kStageBytes/2 apart (leading offset); 8-channel groups 1024 B apart
-      const uint32_t lbo = p.mn_swap ? 1024u : static_cast<uint32_t>(kStageBytes / 2);
-      const uint32_t sbo = p.mn_swap ? static_cast<uint32_t>(kStageBytes / 2) : 1024u;
+      bool ok = true;
       for (long it = 0; it < my_tiles && ok; ++it) {
         if (!sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo)) {
           report_timeout(p.status, kKernelOutProj, 1, -2);
@@ -183,16 +175,13 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             break;
           }
           sm100::tcgen05_fence_after_sync();
-          const uint32_t b_addr = sm100::smem_u32(ring + ps.stage * kStageBytes);
+          const uint32_t a_addr = sm100::smem_u32(ring + ps.stage * C::kStageBytes);
+          const uint64_t db = sm100::umma_desc_kmajor_sw128(a_addr + kTriBytes);
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              // weights: 128 rows x 128 B per M tile inside the K block; tile: 16 channels per MMA = 2 KB
-              const uint64_t da = sm100::umma_desc_kmajor_sw128(w_addr + kb * C::kWBlockBytes + mt * 128 * 128) + 2 * k4;
-              const uint64_t db = sm100::umma_desc_mnmajor_sw128(b_addr + k4 * 2048, lbo, sbo);
-              sm100::umma_bf16_ss(d_tmem + mt * BM, da, db, idesc, (kb | k4) != 0);
-            }
+          for (int k4 = 0; k4 < 4; ++k4) {
+            // tile: 16 channels per MMA = 2 KB; token blocks of 64 are kTriBytes/2 apart, 8-channel groups 1024 B
+            const uint64_t da = sm100::umma_desc_mnmajor_sw128(a_addr + k4 * 2048, kTriBytes / 2, 1024);
+            sm100::umma_bf16_ss(d_tmem, da, db + 2 * k4, idesc, (kb | k4) != 0);
           }
           sm100::umma_commit(&ctl->empty[ps.stage]);
           ps.advance(C::kStages);
@@ -205,6 +194,64 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
       }
     }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------ gate producer (HBM -> box ring)
+    if (lane == 0 && my_tiles > 0) {
+      sm100::tma_prefetch_desc(&tmG);
+      uint32_t seq = 0;
+      bool ok = true;
+      for (long it = 0; it < my_tiles && ok; ++it) {
+        const long m0 = (blockIdx.x + it * gridDim.x) * BM;
+        // boxes in the order the two channel halves consume them (first box of each half first)
+        for (int j = 0; j < C::NBT; ++j) {
+          const int jb = (C::NBT == 4) ? ((j & 1) * 2 + (j >> 1)) : j;
+          const uint32_t sq = seq + jb;
+          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
+          if (!sm100::mbar_wait(&ctl->g_free[slot], ph ^ 1, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelOutProj, 6, jb);
+            ok = false;
+            break;
+          }
+          if (p.debug_skip & 2) {
+            sm100::mbar_arrive(&ctl->g_full[slot]);   // profiling probe: no gate traffic
+          } else {
+            ctl->g_armed[slot] = ph;
+            sm100::mbar_arrive_expect_tx(&ctl->g_full[slot], kBoxBytes);
+            sm100::tma_load_2d(boxes + slot * kBoxBytes, &tmG, &ctl->g_full[slot], jb * 64, static_cast<int>(m0));
+          }
+        }
+        seq += C::NBT;
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ forwarder (finished boxes -> out)
+    if (lane == 0 && my_tiles > 0) {
+      uint32_t seq = 0;
+      bool ok = true;
+      for (long it = 0; it < my_tiles && ok; ++it) {
+        const long m0 = (blockIdx.x + it * gridDim.x) * BM;
+        // the two channel halves finish their boxes side by side: take them in completion order
+        // (first box of each half, then the second), which is also seq order for D = 128
+        for (int j = 0; j < C::NBT; ++j) {
+          const int jb = (C::NBT == 4) ? ((j & 1) * 2 + (j >> 1)) : j;
+          const uint32_t sq = seq + jb;
+          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
+          if (!sm100::mbar_wait(&ctl->o_full[slot], ph, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelOutProj, 7, jb);
+            ok = false;
+            break;
+          }
+          if (!(p.debug_skip & 4)) {
+            sm100::tma_store_2d(&tmO, boxes + slot * kBoxBytes, jb * 64, static_cast<int>(m0));
+          }
+          sm100::tma_store_commit();
+          sm100::tma_store_wait_read<0>();
+          sm100::mbar_arrive(&ctl->g_free[slot]);
+        }
+        seq += C::NBT;
+      }
+      sm100::tma_store_wait_all<0>();
+    }
   } else if (warp >= kStatWarp0) {
     // ------------------------------------------------------------ statistics (8 warps)
     const int st_tid = threadIdx.x - kStatWarp0 * 32;  // 0..255
@@ -212,7 +259,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const int cs = st_tid >> 6;                        // channel subgroup: 16 of every 64 channels
     const int t0 = 2 * pr;
     // byte offset of the pair inside a (64 channels x 64 tokens) box row, before the swizzle
-    const uint32_t blk_off = (t0 >> 6) * (kStageBytes / 2);
+    const uint32_t blk_off = (t0 >> 6) * (kTriBytes / 2);
     const uint32_t chunk16 = (t0 & 63) >> 3;
     const uint32_t in_chunk = (t0 & 7) * 2;
     PipeState ps{0, 0};
@@ -227,7 +274,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           report_timeout(p.status, kKernelOutProj, 3, kb);
           break;
         }
-        const uint8_t* st = ring + ps.stage * kStageBytes + blk_off;
+        const uint8_t* st = ring + ps.stage * C::kStageBytes + blk_off;
         uint32_t v[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
@@ -312,36 +359,15 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     }
   } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------ epilogue (8 warps)
-    // TMEM lane = output channel, column = token.  D = 256: warps 4-7 take channels 0-127, warps
-    // 8-11 channels 128-255, all 128 tokens each.  D = 128: both sets take all channels and split
-    // the tokens 64 / 64.
+    // TMEM lane = token, column = output channel.  Warps 4-7 take the first half of the boxes
+    // (channels), warps 8-11 the second half; a warp owns the 32 token rows of its lane quarter.
     const int quarter = warp & 3;
     const int set = (warp - kEpiWarp0) >> 2;
-    constexpr int MT = D / 128;
-    const int mt = (MT == 2) ? set : 0;
-    constexpr int NTOK = (MT == 2) ? BM : BM / 2;     // tokens this warp handles
-    const int tok0 = (MT == 2) ? 0 : set * NTOK;
-    const int n = mt * 128 + quarter * 32 + lane;      // this lane's output channel
-    const float2 cdn = reinterpret_cast<const float2*>(p.cd)[n];
-    const __nv_bfloat16* gate = static_cast<const __nv_bfloat16*>(p.gate) + n;
-    __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.out) + n;
-    const bool skip_ld = (p.debug_skip & 2) != 0, skip_st = (p.debug_skip & 4) != 0;
-    uint32_t acc = 0, acc_phase = 0;
+    constexpr int NBS = C::NBT / 2;                 // boxes per channel half
+    const int r = quarter * 32 + lane;              // token row inside the tile
+    const int sw = r & 7;
+    uint32_t acc = 0, acc_phase = 0, seq0 = 0;
     for (long it = 0; it < my_tiles; ++it) {
-      const long m0 = (blockIdx.x + it * gridDim.x) * BM + tok0;
-      const int nvalid = static_cast<int>(p.rows - m0 < NTOK ? (p.rows - m0 > 0 ? p.rows - m0 : 0) : NTOK);
-      // gate values of the first 16 tokens are requested before the accumulator is ready.  Loads are
-      // unconditional (a token index past the end is clamped to the last valid one) so that all 16
-      // are in flight together; only the stores are predicated.
-      const int last = nvalid - 1;
-      const bool do_ld = nvalid > 0 && !skip_ld;
-      uint32_t gcur[16], gnext[16];
-#pragma unroll
-      for (int e = 0; e < 16; ++e) gcur[e] = gnext[e] = 0;
-      if (do_ld) {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) gcur[e] = ldg_nc_u16(gate + (m0 + (e < last ? e : last)) * D);
-      }
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = ok && sm100::mbar_wait(&ctl->stats_ready[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
@@ -350,39 +376,71 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         break;
       }
       sm100::tcgen05_fence_after_sync();
-      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D + mt * BM + tok0;
-      const float2* stat = &ctl->stat[acc][tok0];
-      // TMEM reads and gate loads are software-pipelined one 16-token group ahead
+      const float2 rs = ctl->stat[acc][r];  // (rstd, -mean * rstd) of this thread's token
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
       if (!(p.debug_skip & 8)) {
+        // TMEM reads are software-pipelined one 16-channel group ahead, across the boxes of the half
         uint32_t pa[16], pb[16];
-        sm100::tmem_ld_32x32b_x16(trow, pa);
+        sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64, pa);
 #pragma unroll
-        for (int g = 0; g < NTOK / 16; ++g) {
-          sm100::tmem_ld_wait();
-          if (g + 1 < NTOK / 16) {
-            if ((g & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pb);
-            else sm100::tmem_ld_32x32b_x16(trow + (g + 1) * 16, pa);
-            if (do_ld) {
+        for (int i = 0; i < NBS; ++i) {
+          const int jb = set * NBS + i;
+          const uint32_t sq = seq0 + jb;
+          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
+          ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            report_timeout(p.status, kKernelOutProj, 8, jb);
+            break;
+          }
+          uint8_t* row = boxes + slot * kBoxBytes + r * 128;
 #pragma unroll
-              for (int e = 0; e < 16; ++e) {
-                const int m = (g + 1) * 16 + e;
-                gnext[e] = ldg_nc_u16(gate + (m0 + (m < last ? m : last)) * D);
+          for (int g = 0; g < 4; ++g) {
+            const int gi = i * 4 + g;
+            sm100::tmem_ld_wait();
+            if (gi + 1 < NBS * 4) {
+              if ((gi & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pb);
+              else sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pa);
+            }
+            const float2* cdp = &ctl->cd[jb * 64 + g * 16];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              uint4* slot_ptr = reinterpret_cast<uint4*>(row + (((2 * g + hh) ^ sw) << 4));
+              const uint4 gt = *slot_ptr;
+              const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
+              uint32_t ow[4];
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) {
+                const int e = hh * 8 + e2 * 2;
+                const float4 cd2 = *reinterpret_cast<const float4*>(cdp + e);  // (c, d) of two channels, same for all lanes
+                const float a0 = __uint_as_float((gi & 1) == 0 ? pa[e] : pb[e]);
+                const float a1 = __uint_as_float((gi & 1) == 0 ? pa[e + 1] : pb[e + 1]);
+                const float y0 = fmaf(a0, rs.x, fmaf(rs.y, cd2.x, cd2.y));
+                const float y1 = fmaf(a1, rs.x, fmaf(rs.y, cd2.z, cd2.w));
+                ow[e2] = sm100::pack_bf16x2(y0 * sm100::bf16_lo(gw[e2]), y1 * sm100::bf16_hi(gw[e2]));
               }
+              *slot_ptr = make_uint4(ow[0], ow[1], ow[2], ow[3]);
             }
           }
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int m = g * 16 + e;
-            const float2 rs = stat[m];  // (rstd, -mean * rstd), same address for every lane
-            const float accv = __uint_as_float((g & 1) == 0 ? pa[e] : pb[e]);
-            const float y = fmaf(accv, rs.x, fmaf(rs.y, cdn.x, cdn.y));
-            const float gv = __uint_as_float(gcur[e] << 16);
-            if (m < nvalid && !skip_st) outp[(m0 + m) * D] = __float2bfloat16_rn(y * gv);
-          }
-#pragma unroll
-          for (int e = 0; e < 16; ++e) gcur[e] = gnext[e];
+          sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk store
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&ctl->o_full[slot]);
         }
+        if (!ok) break;
+      } else {
+        // profiling probe: no epilogue work, the boxes pass through untouched
+        for (int i = 0; i < NBS; ++i) {
+          const uint32_t sq = seq0 + set * NBS + i;
+          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
+          ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&ctl->o_full[slot]);
+        }
+        if (!ok) break;
       }
+      seq0 += C::NBT;
       sm100::tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
@@ -396,18 +454,21 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   // ------------------------------------------------------------------ teardown
   __syncwarp();  // single-lane roles reconverge with their warp
   __syncthreads();
-  if (warp == 0 && lane == 0 && w_armed) {
-    // let TMA copies still in flight land before the CTA exits (only matters after an expired wait)
-    const uint64_t t0 = sm100::globaltimer_ns();
-    while (!sm100::mbar_test(&ctl->w_full, 0) && sm100::globaltimer_ns() - t0 < 2000000ull) {
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // let TMA copies still in flight land before the CTA exits (only after an expired wait)
+    for (int s = 0; s < C::kStages; ++s) {
+      const uint32_t ph = ctl->armed[s];
+      if (ph != 2) {
+        const uint64_t t1 = sm100::globaltimer_ns();
+        while (!sm100::mbar_test(&ctl->full[s], ph) && sm100::globaltimer_ns() - t1 < 2000000ull) {
+        }
+      }
     }
-    if (*abort_flag != 0) {
-      for (int s = 0; s < C::kStages; ++s) {
-        const uint32_t ph = ctl->armed[s];
-        if (ph != 2) {
-          const uint64_t t1 = sm100::globaltimer_ns();
-          while (!sm100::mbar_test(&ctl->full[s], ph) && sm100::globaltimer_ns() - t1 < 2000000ull) {
-          }
+    for (int s = 0; s < kBoxSlots; ++s) {
+      const uint32_t ph = ctl->g_armed[s];
+      if (ph != 2) {
+        const uint64_t t1 = sm100::globaltimer_ns();
+        while (!sm100::mbar_test(&ctl->g_full[s], ph) && sm100::globaltimer_ns() - t1 < 2000000ull) {
         }
       }
     }
@@ -429,22 +490,22 @@ int out_proj_smem_bytes(int D) {
 }
 
 template <int D>
-static cudaError_t launch_t(const CUtensorMap& tmW, const CUtensorMap& tmT, const OutProjArgs& args, int num_sms,
-                            cudaStream_t stream) {
+static cudaError_t launch_t(const CUtensorMap& tmW, const CUtensorMap& tmT, const CUtensorMap& tmG,
+                            const CUtensorMap& tmO, const OutProjArgs& args, int num_sms, cudaStream_t stream) {
   cudaError_t e =
       cudaFuncSetAttribute(out_proj_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
   if (e != cudaSuccess) return e;
   const long total = (args.rows + BM - 1) / BM;
   if (total <= 0) return cudaSuccess;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
-  out_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, tmT, args);
+  out_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, tmT, tmG, tmO, args);
   return cudaGetLastError();
 }
 
-cudaError_t launch_out_proj(const CUtensorMap& tmW, const CUtensorMap& tmT, const OutProjArgs& args, int num_sms,
-                            cudaStream_t stream) {
-  if (args.D == 128) return launch_t<128>(tmW, tmT, args, num_sms, stream);
-  if (args.D == 256) return launch_t<256>(tmW, tmT, args, num_sms, stream);
+cudaError_t launch_out_proj(const CUtensorMap& tmW, const CUtensorMap& tmT, const CUtensorMap& tmG,
+                            const CUtensorMap& tmO, const OutProjArgs& args, int num_sms, cudaStream_t stream) {
+  if (args.D == 128) return launch_t<128>(tmW, tmT, tmG, tmO, args, num_sms, stream);
+  if (args.D == 256) return launch_t<256>(tmW, tmT, tmG, tmO, args, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -476,6 +476,17 @@ int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, c
     rc = make_tmap(&tmT, tri_local, 2, dims, strides, box);
     if (rc != TRIMUL_OK) return rc;
   }
+  CUtensorMap tmG, tmO;
+  {
+    // gate and out, token-major (rows, D): boxes of 64 channels x 128 tokens (128-byte rows)
+    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(d.rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+    const uint32_t box[2] = {64, 128};
+    rc = make_tmap(&tmG, gate, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+    rc = make_tmap(&tmO, out, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
   trimul::OutProjArgs a;
   memset(&a, 0, sizeof(a));
   a.gate = gate;
@@ -485,10 +496,9 @@ int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, c
   a.D = D;
   a.rows = d.rows;
   a.debug_skip = (debug_skip_bits() >> 4) & 15;
-  a.mn_swap = (debug_skip_bits() >> 8) & 1;
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_out_proj(tmW, tmT, a, num_sms_current(), stream);
+  cudaError_t e = trimul::launch_out_proj(tmW, tmT, tmG, tmO, a, num_sms_current(), stream);
   if (e != cudaSuccess) return cuda_fail(e, "ln_out_proj launch");
   return TRIMUL_OK;
 }

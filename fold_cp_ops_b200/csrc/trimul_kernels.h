@@ -90,21 +90,21 @@ cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, 
 // K_C  output LayerNorm + output projection, gated
 // ---------------------------------------------------------------------------------------------
 struct OutProjArgs {
-  const void* gate;      // bf16 (rows, D)
+  const void* gate;      // bf16 (rows, D); read through tmG
   const float* cd;       // (D, 2) fp32: c[n] = sum_k bf16(gamma_k W[n,k]),  d[n] = sum_k beta_k W[n,k] + b[n]
   void* out;             // bf16 (rows, D)
   float eps;
   int D;
   long rows;
-  int debug_skip;        // profiling aid: bit1 skip gate loads, bit2 skip out stores
-  int mn_swap;           // diagnostic: exchange the two strides of the token-major operand descriptor
+  int debug_skip;        // profiling aid: bit1 skip gate loads, bit2 skip out stores, bit3 skip the epilogue math
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
 
 int out_proj_smem_bytes(int D);
-// tmW: folded weights bf16 (D, D) K-major, box (64, D); tmT: tri as (tokens, channels), box (64, 64)
-cudaError_t launch_out_proj(const CUtensorMap& tmW, const CUtensorMap& tmT, const OutProjArgs& args, int num_sms,
-                            cudaStream_t stream);
+// tmW: folded weights bf16 (D, D) K-major, box (64, D); tmT: tri as (tokens, channels), box (64, 64);
+// tmG / tmO: gate and out as (D, rows), box (64 channels, 128 tokens), 128-byte swizzle
+cudaError_t launch_out_proj(const CUtensorMap& tmW, const CUtensorMap& tmT, const CUtensorMap& tmG,
+                            const CUtensorMap& tmO, const OutProjArgs& args, int num_sms, cudaStream_t stream);
 
 }  // namespace trimul
