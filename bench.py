@@ -319,23 +319,78 @@ def run_ours(args):
         stage_ms = {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
     clocks = sampler.stop() if sampler else None
     # ---- e2e: pinned host -> device, forward, device -> pinned host, every step -----------------
-    ms_e2e = float("nan")
+    # Serial form first (copy in, forward, copy out on one stream: the latency of one request), then the
+    # form a throughput-minded caller uses: the same three operations of every step on three streams with
+    # double-buffered device inputs, so that the copy-in of step i+1 and the copy-out of step i-1 overlap
+    # the forward of step i (PCIe is full duplex).  Every step still moves all of its input and output.
+    ms_e2e = ms_e2e_serial = float("nan")
     if not args.kernels_only:
         step_e2e()
         barrier()
+        n_serial = min(2, args.steps)
         ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         ev2[0].record()
-        for _ in range(args.steps):
+        for _ in range(n_serial):
             step_e2e()
         ev2[1].record()
         barrier()
-        ms_e2e = ev2[0].elapsed_time(ev2[1]) / args.steps
+        ms_e2e_serial = ev2[0].elapsed_time(ev2[1]) / n_serial
+
+        main = torch.cuda.current_stream()
+        s_in, s_fw, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        xd = [torch.empty_like(x_dev) for _ in range(2)]
+        md = [torch.empty_like(m_dev) for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        fw_done = [torch.cuda.Event() for _ in range(2)]
+        for st in (s_in, s_fw, s_out):
+            st.wait_stream(main)
+
+        def step_pipelined(i):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(fw_done[b])          # the forward that read this input buffer has finished
+                xd[b].copy_(x_host, non_blocking=True)
+                md[b].copy_(m_host, non_blocking=True)
+                in_ready[b].record(s_in)
+            with torch.cuda.stream(s_fw):
+                s_fw.wait_event(in_ready[b])
+                o = trimul(wrap(xd[b], (B, N, N, D)), wrap(md[b], (B, N, N)))
+                ol = o.to_local() if cp > 1 else o
+                fw_done[b].record(s_fw)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(fw_done[b])
+                ol.record_stream(s_out)
+                out_host.copy_(ol, non_blocking=True)
+
+        def drain():
+            for st in (s_in, s_fw, s_out):
+                main.wait_stream(st)
+            barrier()
+
+        step_pipelined(0)
+        step_pipelined(1)
+        drain()
+        ev3 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for st in (s_in, s_fw, s_out):
+            st.wait_stream(main)
+        ev3[0].record(main)
+        for st in (s_in, s_fw, s_out):
+            st.wait_stream(main)
+        n_pipe = max(args.steps, 4)
+        for i in range(n_pipe):
+            step_pipelined(i)
+        for st in (s_in, s_fw, s_out):
+            main.wait_stream(st)
+        ev3[1].record(main)
+        barrier()
+        ms_e2e = ev3[0].elapsed_time(ev3[1]) / n_pipe
+        del xd, md
     # ---- reduce over ranks (max) ----------------------------------------------------------------
-    t = torch.tensor([ms, ms_e2e] + ([stage_ms[k] for k in ("ln_gated_proj", "tri_contract", "ln_out_proj")]
-                                     if stage_ms else [0, 0, 0]), device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, ms_e2e, ms_e2e_serial] + ([stage_ms[k] for k in ("ln_gated_proj", "tri_contract", "ln_out_proj")]
+                                                    if stage_ms else [0, 0, 0]), device=dev, dtype=torch.float64)
     if cp > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e, t_a, t_b, t_c = t.tolist()
+    ms, ms_e2e, ms_e2e_serial, t_a, t_b, t_c = t.tolist()
     if eng is not None:
         eng.check()
     # ---- parity spot check at full size: a sampled output tile against the oracle --------------
@@ -378,7 +433,11 @@ def run_ours(args):
                        "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed"},
             "clocks": clocks,
             "e2e": {"value": fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
+                    "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
+                    "mode": "every step copies its input from pinned host memory and its output back; copy-in, "
+                            "forward and copy-out of consecutive steps overlap on three streams",
+                    "serial_ms_per_step": ms_e2e_serial,
+                    "serial_value": fl / (ms_e2e_serial * 1e-3) / 1e12},
             "gpu_launches": args.steps * (3 if cp == 1 else 9),
             "roofline": roof, "cpu_baseline": cpu,
         }
