@@ -415,6 +415,23 @@ def run_ours(args):
                 "peak_source": f"{peaks['source']} (sustained: the kernel runs inside a long step)",
                 "frac_of_burst_peak": (ach / peaks["bf16_tflops"]) if ach else None,
                 "stage_ms": {"ln_gated_proj": t_a, "tri_contract": t_b, "ln_out_proj": t_c}}
+        # whole-step roofline: the slowest of tensor time, HBM time (9 S per rank) and NVLink egress (3 S (cp-1)/cp)
+        S = B * N * N * D * 2.0 / cp
+        t_tc = fl / cp / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        t_hbm = 9.0 * S / (peaks["hbm_gbs"] * 1e9) * 1e3
+        t_nvl = 3.0 * S * (cp - 1) / cp / 770e9 * 1e3
+        roof["step"] = {"roof_ms": max(t_tc, t_hbm, t_nvl), "tensor_ms": t_tc, "hbm_ms": t_hbm, "nvlink_ms": t_nvl,
+                        "frac": max(t_tc, t_hbm, t_nvl) / ms,
+                        "frac_of_burst_tensor_peak": fl / cp / (peaks["bf16_tflops"] * 1e12) * 1e3 / ms,
+                        "note": "tensor term against the measured sustained bf16 rate, HBM against the measured copy "
+                                "rate, NVLink against the measured 770 GB/s peer copy per direction"}
+        if cp > 1 and t_a > 0 and t_b > 0:
+            # the reshards ride the two store epilogues: bytes this rank sends to peers / kernel time
+            roof["nvlink_gbs"] = {"front_in_ln_gated_proj": 2.0 * S * (cp - 1) / cp / (t_a * 1e-3) / 1e9,
+                                  "back_in_tri_contract": S * (cp - 1) / cp / (t_b * 1e-3) / 1e9,
+                                  "exposed_ms": max(0.0, ms - (t_a + t_b + t_c)),
+                                  "note": "egress per rank; exposed = step time not covered by the three kernels "
+                                          "(flag kernels and rank skew; no separate all-to-all runs)"}
         cpu = None
         if not args.kernels_only:
             cores = os.cpu_count() or 1
