@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused TriMul forward on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|nccl_baseline]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload: the README shape of the reference -- z (1, 4096, 4096, 256) bf16 ~ N(0,1), outgoing,
@@ -17,6 +17,8 @@ times the CPU oracle (a port of the reference's eager TriMul) on a bounded sampl
 
 ``--impl reference`` times the reference's eager PyTorch TriMul on the host cores (the reference's
 fused kernels are SM90-only and refuse to run on sm_100), on a bounded sample of the workload.
+``--impl nccl_baseline`` runs the conventional context-parallel form (eager PyTorch kernels + NCCL
+all-gather / reduce-scatter, ``baseline/nccl_cp_trimul.py``) on the same workload and GPUs.
 """
 from __future__ import annotations
 
@@ -214,6 +216,66 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_nccl_baseline(args):
+    """--impl nccl_baseline: eager PyTorch kernels + NCCL collectives (baseline/nccl_cp_trimul.py) on the same
+    workload and GPUs: the conventional context-parallel form the fused path is compared with on this box."""
+    import torch.distributed as dist
+
+    from baseline.nccl_cp_trimul import NcclCpTriMul
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, N, _, D = WORKLOADS[args.workload]
+    n_loc = N // world
+    w = make_layer_weights(D, 0, dev)
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    x = torch.empty(B, n_loc, N, D, dtype=torch.bfloat16, device=dev)
+    chunk = max(1, n_loc // 8)
+    for i0 in range(0, n_loc, chunk):
+        x[:, i0:i0 + chunk] = torch.randn(B, min(chunk, n_loc - i0), N, D, generator=gen).to(torch.bfloat16).to(dev)
+    m = torch.ones(B, n_loc, N, dtype=torch.bfloat16, device=dev)
+    mod = NcclCpTriMul(w)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    n_warm = max(3, args.warmup)
+    for _ in range(n_warm):
+        out = mod.forward(x, args.direction, m)
+    del out
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(args.steps):
+        out = mod.forward(x, args.direction, m)
+    ev[1].record()
+    barrier()
+    t = torch.tensor([ev[0].elapsed_time(ev[1]) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        fl = flops(B, N, D)
+        print(json.dumps({
+            "impl": "nccl_baseline", "metric": "trimul_fwd_tflops", "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "N": N, "D": D, "direction": args.direction,
+                       "parallelism": f"cp{world}", "note": "eager PyTorch kernels + NCCL all-gather / reduce-scatter"},
+            "gpu_launches": 0}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_ours(args):
@@ -506,7 +568,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--impl", choices=("ours", "reference", "nccl_baseline"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="readme_n4096_d256")
     ap.add_argument("--direction", choices=("outgoing", "incoming"), default="outgoing")
     ap.add_argument("--kernels-only", action="store_true",
@@ -516,6 +578,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "nccl_baseline":
+        run_nccl_baseline(args)
     else:
         run_ours(args)
 
