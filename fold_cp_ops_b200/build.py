@@ -17,7 +17,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libtrimul_sm100.so"
 
-SOURCES = ("trimul_capi.cu", "ln_gated_proj.cu", "tri_contract.cu", "ln_out_proj.cu", "peer_sync.cu",
+SOURCES = ("trimul_capi.cu", "ln_gated_proj.cu", "tri_contract.cu", "tri_contract_pair.cu", "ln_out_proj.cu", "peer_sync.cu",
            "forward_static.cu")
 HEADERS = ("sm100_ptx.cuh", "trimul_common.cuh", "trimul_kernels.h")
 

@@ -1,0 +1,352 @@
+// Triangle contraction on CTA PAIRS (tcgen05 cta_group::2): the same computation as
+// tri_contract.cu,
+//     T_l[i, j] = sum_k  A_l[i, k] * B_l[j, k]          (bf16 in, fp32 accumulate, bf16 out)
+// with a 256 x 256 output tile per pair of CTAs on neighbouring SMs.  Each CTA loads its own 128
+// rows of A and HALF of the 256 B rows; one thread of the pair's first CTA issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads A from each CTA's own shared memory and the two
+// B halves from both, and leaves rows [128 r, 128 r + 128) of the tile in CTA r's TMEM.  Per FLOP
+// that is two thirds of the L2 -> SM traffic and half of the B-operand shared-memory reads of the
+// single-CTA 128 x 256 tile, and the smaller stages make the ring six deep.
+//
+// Barriers: every CTA waits only on barriers in its own shared memory.  The operand loads of
+// both CTAs complete on the FIRST CTA's `full` barrier (cp.async.bulk.tensor .cta_group::2 lets a
+// load signal the peer's barrier; no multicast load anywhere); tcgen05.commit releases a stage /
+// publishes an accumulator in BOTH CTAs at once; the second CTA's epilogue warps hand the
+// accumulator back with a remote arrive on the first CTA's `tmem_empty`.  All waits are bounded as
+// in the single-CTA kernel.
+#include "trimul_common.cuh"
+#include "trimul_kernels.h"
+
+namespace trimul {
+
+namespace {
+
+constexpr int BM = 128;          // rows per CTA
+constexpr int BN = 256;          // columns per pair
+constexpr int BNH = BN / 2;      // B rows each CTA loads
+constexpr int BK = 64;
+constexpr int kStages = 6;
+constexpr int kABytes = BM * BK * 2;    // 16 KB
+constexpr int kBBytes = BNH * BK * 2;   // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 192;  // warp 0 TMA, warp 1 MMA (first CTA) + TMEM alloc, warps 2..5 epilogue
+constexpr int kOutCols = 64;
+constexpr int kOutBufBytes = 32 * kOutCols * 2;
+constexpr int kOutStageBytes = 4 * 2 * kOutBufBytes;
+
+struct SmemCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
+
+// ---- cluster / pair PTX -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_mbar_init_cluster() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tiled load whose completion bytes go to a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(sm100::smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm100::smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (once all MMAs issued so far have retired) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   sm100::smem_u32(bar)),
+               "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+
+}  // namespace
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ TriOutMaps out_maps, const TriContractArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* out_stage = tiles + kStages * kStageBytes;
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(out_stage + kOutStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();          // 0: first CTA of the pair (issues the MMAs), 1: second
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_i = (p.n_i + 2 * BM - 1) / (2 * BM);
+  const int tiles_j = (p.n_j + BN - 1) / BN;
+  const int tiles_per_plane = tiles_i * tiles_j;
+  const long total_tiles = static_cast<long>(tiles_per_plane) * p.planes;
+  const int num_k = (p.n_k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      sm100::mbar_init(&ctl->full[s], 1);    // first CTA: its producer's arrive + the bytes of both CTAs' loads
+      sm100::mbar_init(&ctl->empty[s], 1);   // tcgen05.commit, delivered to both CTAs
+    }
+    for (int a = 0; a < 2; ++a) {
+      sm100::mbar_init(&ctl->tmem_full[a], 1);
+      sm100::mbar_init(&ctl->tmem_empty[a], 8);  // four epilogue warps of each CTA (counted in the first CTA)
+    }
+    ctl->abort_flag = 0;
+    fence_mbar_init_cluster();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&ctl->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  sm100::tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals the peer
+  sm100::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const uint64_t tmo = p.timeout_ns;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      sm100::tma_prefetch_desc(&tmA);
+      sm100::tma_prefetch_desc(&tmB);
+      PipeState ps{0, 0};
+      for (long t = pair; t < total_tiles; t += num_pairs) {
+        const int plane = static_cast<int>(t / tiles_per_plane);
+        const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
+        const int ti = r / tiles_j;
+        const int tj = r - ti * tiles_j;
+        bool ok = true;
+        for (int kc = 0; kc < num_k; ++kc) {
+          if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelTriContract, 0, kc);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + ps.stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          // both CTAs' bytes are counted on the first CTA's barrier
+          const uint32_t bar = map_to_cta(sm100::smem_u32(&ctl->full[ps.stage]), 0);
+          if (cta == 0) sm100::mbar_arrive_expect_tx(&ctl->full[ps.stage], 2 * kStageBytes);
+          tma_load_3d_pair(sa, &tmA, bar, kc * BK, ti * 2 * BM + static_cast<int>(cta) * BM, plane);
+          tma_load_3d_pair(sb, &tmB, bar, kc * BK, tj * BN + static_cast<int>(cta) * BNH, plane);
+          ps.advance(kStages);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- UMMA issuer (first CTA only)
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(2 * BM, BN);
+      PipeState ps{0, 0};
+      uint32_t acc = 0, acc_phase = 0;
+      for (long t = pair; t < total_tiles; t += num_pairs) {
+        bool ok = sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo);
+        if (!ok) {
+          report_timeout(p.status, kKernelTriContract, 1, -1);
+          break;
+        }
+        sm100::tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kc = 0; kc < num_k; ++kc) {
+          if (!sm100::mbar_wait(&ctl->full[ps.stage], ps.phase, abort_flag, tmo)) {
+            report_timeout(p.status, kKernelTriContract, 1, kc);
+            ok = false;
+            break;
+          }
+          sm100::tcgen05_fence_after_sync();
+          const uint32_t sa = sm100::smem_u32(tiles + ps.stage * kStageBytes);
+          const uint64_t da = sm100::umma_desc_kmajor_sw128(sa);
+          const uint64_t db = sm100::umma_desc_kmajor_sw128(sa + kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            umma_bf16_ss_pair(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0);
+          }
+          umma_commit_pair(&ctl->empty[ps.stage]);  // frees the stage in both CTAs when the MMAs retire
+          ps.advance(kStages);
+        }
+        if (!ok) break;
+        umma_commit_pair(&ctl->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    uint32_t acc = 0, acc_phase = 0, out_par = 0;
+    const long owner_plane_elems = static_cast<long>(p.ni_loc) * p.nj_loc;
+    for (long t = pair; t < total_tiles; t += num_pairs) {
+      const int plane = static_cast<int>(t / tiles_per_plane);
+      const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
+      const int ti = r / tiles_j;
+      const int tj = r - ti * tiles_j;
+      bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        report_timeout(p.status, kKernelTriContract, 2, static_cast<int>(t));
+        break;
+      }
+      sm100::tcgen05_fence_after_sync();
+      const int i0w = ti * 2 * BM + static_cast<int>(cta) * BM + quarter * 32;
+      const int i = i0w + lane;
+      const bool row_ok = i < p.n_i;
+      const int i_blk = row_ok ? i / p.ni_loc : 0;
+      const int i_l = i - i_blk * p.ni_loc;
+      const int iw_blk = i0w / p.ni_loc;
+      const bool band_ok = !p.direct_stores && (i0w + 31 < p.n_i) && ((i0w + 31) / p.ni_loc == iw_blk);
+      const long dst_plane = static_cast<long>(p.chan_offset) * p.batch + plane;
+      const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int cc = 0; cc < BN / kOutCols; ++cc) {
+        uint32_t v[kOutCols];
+        {
+          uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
+          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
+          sm100::tmem_ld_32x32b_x32(taddr_row + cc * kOutCols, lo);
+          sm100::tmem_ld_32x32b_x32(taddr_row + cc * kOutCols + 32, hi);
+        }
+        const int j0 = tj * BN + cc * kOutCols;
+        const int jw_blk = j0 / p.nj_loc;
+        const bool fast = band_ok && (j0 + kOutCols - 1 < p.n_j) && ((j0 + kOutCols - 1) / p.nj_loc == jw_blk);
+        uint8_t* buf = out_stage + ((warp - 2) * 2 + (out_par & 1)) * kOutBufBytes;
+        if (fast) {
+          if (lane == 0) sm100::tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        sm100::tmem_ld_wait();
+        if (fast) {
+#pragma unroll
+          for (int q = 0; q < kOutCols / 8; ++q) {
+            uint4 pk;
+            pk.x = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+            pk.y = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+            pk.z = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+            pk.w = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) = pk;
+          }
+          sm100::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            sm100::tma_store_3d(&out_maps.map[iw_blk * p.cp1 + jw_blk], buf, j0 - jw_blk * p.nj_loc,
+                                i0w - iw_blk * p.ni_loc, static_cast<int>(dst_plane));
+            sm100::tma_store_commit();
+          }
+          ++out_par;
+        } else if (row_ok && j0 < p.n_j) {
+#pragma unroll
+          for (int q = 0; q < kOutCols / 8; ++q) {
+            const int j = j0 + q * 8;
+            if (j < p.n_j) {
+              const int j_blk = j / p.nj_loc;
+              const int j_l = j - j_blk * p.nj_loc;
+              __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.out.ptr[i_blk * p.cp1 + j_blk]);
+              uint4 pk;
+              pk.x = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(base + dst_plane * owner_plane_elems + static_cast<long>(i_l) * p.nj_loc +
+                                        j_l) = pk;
+            }
+          }
+        }
+      }
+      // hand the accumulator back: the count lives in the first CTA
+      sm100::tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(sm100::smem_u32(&ctl->tmem_empty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if (lane == 0) sm100::tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // a wait expired: give loads still in flight (this CTA's and the peer's) time to land
+    const uint64_t t0 = sm100::globaltimer_ns();
+    while (sm100::globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  sm100::tcgen05_fence_before_sync();
+  cluster_sync_all();   // neither CTA retires while the other may still signal it or read its operand half
+  if (warp == 1) {
+    sm100::tcgen05_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+cudaError_t launch_tri_contract_pair(const CUtensorMap& tmA, const CUtensorMap& tmBhalf, const TriOutMaps& out_maps,
+                                     const TriContractArgs& args, int num_sms, cudaStream_t stream) {
+  cudaError_t e =
+      cudaFuncSetAttribute(tri_contract_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int tiles_i = (args.n_i + 2 * BM - 1) / (2 * BM);
+  const int tiles_j = (args.n_j + BN - 1) / BN;
+  const long total = static_cast<long>(tiles_i) * tiles_j * args.planes;
+  if (total <= 0) return cudaSuccess;
+  const long pairs = num_sms / 2;
+  const int grid = 2 * static_cast<int>(total < pairs ? total : pairs);
+  tri_contract_pair_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmBhalf, out_maps, args);
+  return cudaGetLastError();
+}
+
+}  // namespace trimul

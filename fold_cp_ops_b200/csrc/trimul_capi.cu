@@ -446,7 +446,21 @@ int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, v
   }
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_tri_contract(tmA, tmB, out_maps, a, num_sms_current(), stream);
+  cudaError_t e;
+  if (!((debug_skip_bits() >> 14) & 1) && num_sms_current() >= 2) {
+    // CTA-pair form (256 x 256 tile per pair of SMs; bit 14 of the profiling mask selects the
+    // single-CTA 128 x 256 kernel instead): B is loaded in two halves of 128 rows
+    CUtensorMap tmBh;
+    const uint64_t dims[3] = {n, n, planes};
+    const uint64_t strides[2] = {n * 2, n * n * 2};
+    const uint32_t boxH[3] = {64, 128, 1};
+    const uint8_t* b_base = static_cast<const uint8_t*>(ab_local) + planes * n * n * 2;
+    rc = make_tmap(&tmBh, b_base, 3, dims, strides, boxH);
+    if (rc != TRIMUL_OK) return rc;
+    e = trimul::launch_tri_contract_pair(tmA, tmBh, out_maps, a, num_sms_current(), stream);
+  } else {
+    e = trimul::launch_tri_contract(tmA, tmB, out_maps, a, num_sms_current(), stream);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "tri_contract launch");
   return TRIMUL_OK;
 }

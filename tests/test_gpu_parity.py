@@ -213,6 +213,28 @@ def test_kernel_tri_contract(N, planes_d):
     assert (err <= 2.0 ** -8 * want.abs() + 1e-3 * want.abs().max()).all(), err.max().item()
 
 
+@pytest.mark.parametrize("N", [8, 200, 512])
+def test_kernel_tri_contract_pair_form_equals_single_cta_form(N, monkeypatch):
+    """The default contraction kernel works on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); the
+    single-CTA 128 x 256 kernel stays selectable.  Same K order, same fp32 accumulation: bitwise equal."""
+    from fold_cp_ops_b200 import kernels as K
+
+    torch.manual_seed(7 + N)
+    D = 128
+    ab = (0.5 * torch.randn(2, D, 1, N, N, device=DEV)).to(torch.bfloat16)
+    outs = []
+    for bits in ("0", "16384"):
+        monkeypatch.setenv("TRIMUL_DEBUG_SKIP", bits)
+        tri = torch.full((D, 1, N, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        st = K.new_status(DEV)
+        K.tri_contract(K.make_geom(1, N, D, "outgoing", 1e-5), ab, [tri.data_ptr()], st)
+        torch.cuda.synchronize()
+        K.check_status(st)
+        outs.append(tri)
+    assert not torch.isnan(outs[0].float()).any()
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0)])
 def test_kernel_ln_out_proj(D, B, n, offset):
     """The folded LayerNorm (rstd * (x W'^T - mean c) + d) against an explicit fp32 LayerNorm; the last
