@@ -46,66 +46,6 @@ struct SmemCtl {
 
 constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
 
-// ---- cluster / pair PTX -------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void fence_mbar_init_cluster() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// tiled load whose completion bytes go to a barrier that may live in the peer CTA
-__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(sm100::smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm100::smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                                  uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// arrive (once all MMAs issued so far have retired) on the barrier at this offset in BOTH CTAs
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
-                   sm100::smem_u32(bar)),
-               "h"(static_cast<uint16_t>(3))
-               : "memory");
-}
-
 }  // namespace
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -118,7 +58,7 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t cta = cluster_ctarank();          // 0: first CTA of the pair (issues the MMAs), 1: second
+  const uint32_t cta = sm100::cluster_ctarank();          // 0: first CTA of the pair (issues the MMAs), 1: second
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -138,15 +78,15 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       sm100::mbar_init(&ctl->tmem_empty[a], 8);  // four epilogue warps of each CTA (counted in the first CTA)
     }
     ctl->abort_flag = 0;
-    fence_mbar_init_cluster();
+    sm100::fence_mbar_init_cluster();
   }
   if (warp == 1) {
-    tmem_alloc_pair(&ctl->tmem_base, kTmemCols);
-    tmem_relinquish_pair();
+    sm100::tmem_alloc_pair(&ctl->tmem_base, kTmemCols);
+    sm100::tmem_relinquish_pair();
   }
   sm100::tcgen05_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals the peer
+  sm100::cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals the peer
   sm100::tcgen05_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
@@ -173,10 +113,10 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint8_t* sa = tiles + ps.stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
           // both CTAs' bytes are counted on the first CTA's barrier
-          const uint32_t bar = map_to_cta(sm100::smem_u32(&ctl->full[ps.stage]), 0);
+          const uint32_t bar = sm100::map_to_cta(sm100::smem_u32(&ctl->full[ps.stage]), 0);
           if (cta == 0) sm100::mbar_arrive_expect_tx(&ctl->full[ps.stage], 2 * kStageBytes);
-          tma_load_3d_pair(sa, &tmA, bar, kc * BK, ti * 2 * BM + static_cast<int>(cta) * BM, plane);
-          tma_load_3d_pair(sb, &tmB, bar, kc * BK, tj * BN + static_cast<int>(cta) * BNH, plane);
+          sm100::tma_load_3d_pair(sa, &tmA, bar, kc * BK, ti * 2 * BM + static_cast<int>(cta) * BM, plane);
+          sm100::tma_load_3d_pair(sb, &tmB, bar, kc * BK, tj * BN + static_cast<int>(cta) * BNH, plane);
           ps.advance(kStages);
         }
         if (!ok) break;
@@ -208,13 +148,13 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint64_t db = sm100::umma_desc_kmajor_sw128(sa + kABytes);
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4) {
-            umma_bf16_ss_pair(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0);
+            sm100::umma_bf16_ss_pair(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0);
           }
-          umma_commit_pair(&ctl->empty[ps.stage]);  // frees the stage in both CTAs when the MMAs retire
+          sm100::umma_commit_pair(&ctl->empty[ps.stage]);  // frees the stage in both CTAs when the MMAs retire
           ps.advance(kStages);
         }
         if (!ok) break;
-        umma_commit_pair(&ctl->tmem_full[acc]);
+        sm100::umma_commit_pair(&ctl->tmem_full[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -305,7 +245,7 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       // hand the accumulator back: the count lives in the first CTA
       sm100::tcgen05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_remote(map_to_cta(sm100::smem_u32(&ctl->tmem_empty[acc]), 0));
+      if (lane == 0) sm100::mbar_arrive_remote(sm100::map_to_cta(sm100::smem_u32(&ctl->tmem_empty[acc]), 0));
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -324,10 +264,10 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
   }
   sm100::tcgen05_fence_before_sync();
-  cluster_sync_all();   // neither CTA retires while the other may still signal it or read its operand half
+  sm100::cluster_sync_all();   // neither CTA retires while the other may still signal it or read its operand half
   if (warp == 1) {
     sm100::tcgen05_fence_after_sync();
-    tmem_dealloc_pair(tmem_base, kTmemCols);
+    sm100::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
