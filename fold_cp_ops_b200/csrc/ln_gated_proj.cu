@@ -40,16 +40,14 @@ constexpr int kNumChunks = 5;            // a_lo, a_hi, b_lo, b_hi, gate
 constexpr int kRowPitch = BM * 2;        // bytes per channel row of the a|b staging tile (128 tokens)
 constexpr int kFwdWarp = 3;              // control warp whose lane 0 forwards staged tiles
 
-template <int D, bool PAIR>
+template <int D>
 struct Cfg {
-  static constexpr int NC = PAIR ? 2 : 1;       // CTAs that share one weight stream (tcgen05 cta_group::2 pair)
   static constexpr int CH = D / 2;              // channels per gated chunk
   static constexpr int KB = D / 64;             // 64-wide K blocks
   static constexpr int kABytes = BM * D * 2;    // one operand tile
   static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
-  static constexpr int kWRows = D / NC;         // weight rows of a chunk this CTA loads
-  static constexpr int kWStageBytes = kWRows * 128;  // kWRows weight rows x 64 k
-  static constexpr int kWStages = PAIR ? ((D == 256) ? 6 : 8) : ((D == 256) ? 3 : 4);
+  static constexpr int kWStageBytes = D * 128;  // D weight rows x 64 k
+  static constexpr int kWStages = (D == 256) ? 3 : 4;
   static constexpr int kABufs = (D == 256) ? 1 : 2;
   static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
   static constexpr int kStageBuf = CH * kRowPitch;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or half of the gate tile
@@ -57,10 +55,10 @@ struct Cfg {
   static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes + 2 * kStageBuf;
 };
 
-template <int D, bool PAIR>
+template <int D>
 struct SmemCtl {
-  uint64_t w_full[Cfg<D, PAIR>::kWStages];
-  uint64_t w_empty[Cfg<D, PAIR>::kWStages];
+  uint64_t w_full[Cfg<D>::kWStages];
+  uint64_t w_empty[Cfg<D>::kWStages];
   uint64_t xn_ready[2];
   uint64_t x_empty[2];
   uint64_t tmem_full[2];
@@ -69,12 +67,12 @@ struct SmemCtl {
   uint64_t st_free[2];   // ... and read completely by the forwarder's bulk stores
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
-  volatile uint32_t armed[Cfg<D, PAIR>::kWStages];
+  volatile uint32_t armed[Cfg<D>::kWStages];
 };
 
-template <int D, bool PAIR>
+template <int D>
 constexpr int smem_bytes() {
-  return Cfg<D, PAIR>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D, PAIR>)) + 64;
+  return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
 // Optional device timeline of CTA 0 (profiling aid): (globaltimer << 8 | event id) records.  Each
@@ -182,33 +180,23 @@ __device__ __forceinline__ TileCoord decode_tile(long t, int tiles_per_line, int
 
 }  // namespace
 
-template <int D, bool PAIR>
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ GatedOutMaps om,
                   const GatedProjArgs p) {
-  using C = Cfg<D, PAIR>;
+  using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = tiles;                              // kABufs x kABytes
   uint8_t* w_tiles = tiles + C::kABufs * C::kABytes;     // kWStages x kWStageBytes
   uint8_t* st_tiles = w_tiles + C::kWStages * C::kWStageBytes;  // 2 x kStageBuf
-  SmemCtl<D, PAIR>* ctl = reinterpret_cast<SmemCtl<D, PAIR>*>(tiles + C::kTileBytes);
+  SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   const int tiles_per_line = (p.n_walk + BM - 1) / BM;
   const long total_tiles = static_cast<long>(p.batch) * p.n_lines * tiles_per_line;
-  // Work is dealt in groups of NC consecutive tiles: one tile per CTA, or -- PAIR -- two tiles to a
-  // pair of CTAs on neighbouring SMs that share one weight stream: each CTA loads half of every
-  // weight stage, the first CTA issues tcgen05.mma.cta_group::2 (M = 256) over both operand tiles,
-  // and rows [128 r, 128 r + 128) of the accumulator land in CTA r's TMEM.  A group past the last
-  // tile still runs in the second CTA (its weight half is needed) with all of its rows masked off.
-  constexpr int NC = C::NC;
-  const uint32_t cta = PAIR ? sm100::cluster_ctarank() : 0u;
-  const long grp0 = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
-  const long ngrp = PAIR ? (gridDim.x >> 1) : gridDim.x;
-  const long n_groups = (total_tiles + NC - 1) / NC;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kWStages; ++s) {
@@ -217,29 +205,22 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       ctl->armed[s] = 2;
     }
     for (int a = 0; a < 2; ++a) {
-      sm100::mbar_init(&ctl->xn_ready[a], kLnWarps * NC);    // one arrive per LayerNorm warp (of both CTAs, counted in the first)
+      sm100::mbar_init(&ctl->xn_ready[a], kLnWarps);    // one arrive per LayerNorm warp
       sm100::mbar_init(&ctl->x_empty[a], 1);     // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_full[a], 1);   // tcgen05.commit
-      sm100::mbar_init(&ctl->tmem_empty[a], kEpiWarps * NC);  // one arrive per epilogue warp (of both CTAs)
+      sm100::mbar_init(&ctl->tmem_empty[a], kEpiWarps);  // one arrive per epilogue warp
       sm100::mbar_init(&ctl->st_full[a], kEpiWarps);     // one arrive per epilogue warp
       sm100::mbar_init(&ctl->st_free[a], 1);             // the forwarder
     }
     ctl->abort_flag = 0;
-    if (PAIR) sm100::fence_mbar_init_cluster();
-    else sm100::mbar_init_fence();
+    sm100::mbar_init_fence();
   }
   if (warp == 2) {
-    if (PAIR) {
-      sm100::tmem_alloc_pair(&ctl->tmem_base, C::kTmemCols);
-      sm100::tmem_relinquish_pair();
-    } else {
-      sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
-      sm100::tmem_relinquish();
-    }
+    sm100::tmem_alloc(&ctl->tmem_base, C::kTmemCols);
+    sm100::tmem_relinquish();
   }
   sm100::tcgen05_fence_before_sync();
   __syncthreads();
-  if (PAIR) sm100::cluster_sync_all();  // both CTAs' barriers exist before either signals the other
   sm100::tcgen05_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
@@ -253,7 +234,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       PipeState ps{0, 0};
       uint32_t n_loads = 0;
       bool ok = true;
-      for (long g = grp0; g < n_groups && ok; g += ngrp) {
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int c = 0; c < kNumChunks && ok; ++c) {
           for (int kb = 0; kb < C::KB; ++kb) {
             if (!sm100::mbar_wait(&ctl->w_empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
@@ -267,13 +248,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                                    ((p.debug_skip & 16) && n_loads >= C::kWStages && (n_loads & 1));
             ++n_loads;
             if (skip_load) {
-              if (cta == 0) sm100::mbar_arrive(&ctl->w_full[ps.stage]);
-            } else if (PAIR) {
-              // the halves of both CTAs are counted on the first CTA's barrier
-              const uint32_t bar = sm100::map_to_cta(sm100::smem_u32(&ctl->w_full[ps.stage]), 0);
-              if (cta == 0) sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], NC * C::kWStageBytes);
-              sm100::tma_load_2d_pair(w_tiles + ps.stage * C::kWStageBytes, &tmW, bar, kb * 64,
-                                      c * D + static_cast<int>(cta) * C::kWRows);
+              sm100::mbar_arrive(&ctl->w_full[ps.stage]);
             } else {
               ctl->armed[ps.stage] = ps.phase;
               sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], C::kWStageBytes);
@@ -283,15 +258,15 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
         }
       }
-    } else if (warp == 1 && lane == 0 && cta == 0) {
-      // ---------------------------------------------------------- UMMA issuer (the first CTA of a pair)
-      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM * NC, D);
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------- UMMA issuer
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
       Tracer tr;
       tr.init(0);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
-      for (long g = grp0; g < n_groups && ok; g += ngrp) {
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!sm100::mbar_wait(&ctl->xn_ready[buf], buf_phase, abort_flag, tmo)) {
           report_timeout(p.status, kKernelGatedProj, 1, -1);
           break;
@@ -319,16 +294,13 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const uint64_t db = sm100::umma_desc_kmajor_sw128(sm100::smem_u32(w_tiles + ps.stage * C::kWStageBytes));
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
-              if (PAIR) sm100::umma_bf16_ss_pair(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
-              else sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+              sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
             }
-            if (PAIR) sm100::umma_commit_pair(&ctl->w_empty[ps.stage]);   // frees the stage in both CTAs
-            else sm100::umma_commit(&ctl->w_empty[ps.stage]);
+            sm100::umma_commit(&ctl->w_empty[ps.stage]);
             ps.advance(C::kWStages);
           }
           if (!ok) break;
-          if (PAIR) sm100::umma_commit_pair(&ctl->tmem_full[acc]);
-          else sm100::umma_commit(&ctl->tmem_full[acc]);
+          sm100::umma_commit(&ctl->tmem_full[acc]);
           tr.ev(3);
           if (++acc == 2) {
             acc = 0;
@@ -336,9 +308,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
         }
         if (!ok) break;
-        // operand tile(s) free once every MMA of the group retired
-        if (PAIR) sm100::umma_commit_pair(&ctl->x_empty[buf]);
-        else sm100::umma_commit(&ctl->x_empty[buf]);
+        sm100::umma_commit(&ctl->x_empty[buf]);  // operand tile free once every MMA of the tile retired
         if (++buf == C::kABufs) {
           buf = 0;
           buf_phase ^= 1;
@@ -351,10 +321,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int d_loc_n = 1 << p.d_loc_log2;
       uint32_t use = 0;  // running count of buffer uses; buffer = use & 1, phase = (use >> 1) & 1
       bool ok = true;
-      for (long g = grp0; g < n_groups && ok; g += ngrp) {
-        const long t = g * NC + cta;
-        const bool tile_ok = t < total_tiles;   // false: the masked-off tile of an odd last group
-        const TileCoord tc = decode_tile(tile_ok ? t : 0, tiles_per_line, p.n_lines);
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
         const int dst_x = p.dst_x0 + tc.w0;
         const int dst_y = p.dst_y0 + tc.line;
         for (int c = 0; c < kNumChunks && ok; ++c) {
@@ -371,7 +339,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           if (c < 4) {
             const uint8_t* src = st_tiles + (use & 1) * C::kStageBuf;
             const int h = c >> 1;
-            if (tile_ok && !(p.debug_skip & 1)) {
+            if (!(p.debug_skip & 1)) {
 #pragma unroll 1
               for (int k = 0; k < C::CH / 16; ++k) {
                 const int d = (c & 1) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
@@ -379,7 +347,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                                     h * d_loc_n + (d & d_loc_mask));
               }
             }
-          } else if (tile_ok && !(p.debug_skip & 2)) {
+          } else if (!(p.debug_skip & 2)) {
             const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
             const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
 #pragma unroll 1
@@ -415,10 +383,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     Tracer tr;
     tr.init(1);
     uint32_t buf = 0, buf_phase = 0;
-    for (long g = grp0; g < n_groups; g += ngrp) {
-      const long t = g * NC + cta;
-      const bool tile_ok = t < total_tiles;
-      const TileCoord tc = decode_tile(tile_ok ? t : 0, tiles_per_line, p.n_lines);
+    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
       const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
       // every row of this warp is requested before any is used: 16 x 512 B in flight per warp
       uint4 raw[PASSES];
@@ -426,7 +392,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       for (int ps = 0; ps < PASSES; ++ps) {
         const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
         const int w = tc.w0 + r;
-        if (tile_ok && w < p.n_walk && !(p.debug_skip & 4)) {
+        if (w < p.n_walk && !(p.debug_skip & 4)) {
           raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
         } else {
           raw[ps] = make_uint4(0, 0, 0, 0);
@@ -477,10 +443,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
       __syncwarp();
-      if (lane == 0) {
-        if (PAIR) sm100::mbar_arrive_remote(sm100::map_to_cta(sm100::smem_u32(&ctl->xn_ready[buf]), 0));
-        else sm100::mbar_arrive(&ctl->xn_ready[buf]);
-      }
+      if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
       if (lw == 0 && lane == 0) tr.ev(9);
       if (++buf == C::kABufs) {
         buf = 0;
@@ -498,12 +461,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     tr.init(2);
     uint32_t acc = 0, acc_phase = 0, use = 0;
     bool ok = true;
-    for (long g = grp0; g < n_groups && ok; g += ngrp) {
-      const long t = g * NC + cta;
-      const bool tile_ok = t < total_tiles;
-      const TileCoord tc = decode_tile(tile_ok ? t : 0, tiles_per_line, p.n_lines);
+    for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
       const int w = tc.w0 + r;
-      const bool valid = tile_ok && w < p.n_walk;
+      const bool valid = w < p.n_walk;
       const long srow = tc.b * p.batch_rows + tc.line * p.line_rows + static_cast<long>(w) * p.walk_rows;
       float mval = 1.0f;
       if (valid && p.mask_kind != 0) {
@@ -572,8 +533,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk stores
         __syncwarp();
         if (lane == 0) {
-          if (PAIR) sm100::mbar_arrive_remote(sm100::map_to_cta(sm100::smem_u32(&ctl->tmem_empty[acc]), 0));
-          else sm100::mbar_arrive(&ctl->tmem_empty[acc]);
+          sm100::mbar_arrive(&ctl->tmem_empty[acc]);
           for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_full[(use + u) & 1]);
         }
         use += n_use;
@@ -590,31 +550,19 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   __syncwarp();  // single-lane roles reconverge with their warp
   __syncthreads();
   if (*abort_flag != 0 && threadIdx.x == 0) {
-    // a wait expired: let weight loads still in flight land before the CTA retires
-    if (PAIR) {
-      const uint64_t t0 = sm100::globaltimer_ns();
-      while (sm100::globaltimer_ns() - t0 < 200000ull) {
-      }
-    } else {
-      for (int s = 0; s < C::kWStages; ++s) {
-        const uint32_t ph = ctl->armed[s];
-        if (ph != 2) {
-          const uint64_t t0 = sm100::globaltimer_ns();
-          while (!sm100::mbar_test(&ctl->w_full[s], ph) && sm100::globaltimer_ns() - t0 < 2000000ull) {
-          }
+    for (int s = 0; s < C::kWStages; ++s) {
+      const uint32_t ph = ctl->armed[s];
+      if (ph != 2) {
+        const uint64_t t0 = sm100::globaltimer_ns();
+        while (!sm100::mbar_test(&ctl->w_full[s], ph) && sm100::globaltimer_ns() - t0 < 2000000ull) {
         }
       }
     }
   }
   __syncthreads();
-  if (PAIR) {
-    sm100::tcgen05_fence_before_sync();
-    sm100::cluster_sync_all();  // neither CTA retires while the other may still signal it or read its weight half
-  }
   if (warp == 2) {
     sm100::tcgen05_fence_after_sync();
-    if (PAIR) sm100::tmem_dealloc_pair(tmem_base, C::kTmemCols);
-    else sm100::tmem_dealloc(tmem_base, C::kTmemCols);
+    sm100::tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -632,47 +580,29 @@ extern "C" int trimul_debug_set_gated_proj_trace(void* buf, unsigned int cap) {
 }
 
 int gated_proj_smem_bytes(int D) {
-  if (D == 128) return smem_bytes<128, true>();
-  if (D == 256) return smem_bytes<256, true>();
+  if (D == 128) return smem_bytes<128>();
+  if (D == 256) return smem_bytes<256>();
   return -1;
 }
 
-template <int D, bool PAIR>
+template <int D>
 static cudaError_t launch_t(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
                             cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(gated_proj_kernel<D, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       smem_bytes<D, PAIR>());
+  cudaError_t e =
+      cudaFuncSetAttribute(gated_proj_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
   if (e != cudaSuccess) return e;
   const int tiles_per_line = (args.n_walk + BM - 1) / BM;
   const long total = static_cast<long>(args.batch) * args.n_lines * tiles_per_line;
   if (total <= 0) return cudaSuccess;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cudaLaunchAttribute attr[1];
-  if (PAIR) {
-    const long groups = (total + 1) / 2, pairs = num_sms / 2;
-    cfg.gridDim = dim3(2 * static_cast<unsigned>(groups < pairs ? groups : pairs));
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  } else {
-    cfg.gridDim = dim3(static_cast<unsigned>(total < num_sms ? total : num_sms));
-  }
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem_bytes<D, PAIR>();
-  cfg.stream = stream;
-  return cudaLaunchKernelEx(&cfg, gated_proj_kernel<D, PAIR>, tmW, maps, args);
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  gated_proj_kernel<D><<<grid, kThreads, smem_bytes<D>(), stream>>>(tmW, maps, args);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
-                              bool pair, cudaStream_t stream) {
-  if (args.D == 128) return pair ? launch_t<128, true>(tmW, maps, args, num_sms, stream)
-                                 : launch_t<128, false>(tmW, maps, args, num_sms, stream);
-  if (args.D == 256) return pair ? launch_t<256, true>(tmW, maps, args, num_sms, stream)
-                                 : launch_t<256, false>(tmW, maps, args, num_sms, stream);
+                              cudaStream_t stream) {
+  if (args.D == 128) return launch_t<128>(tmW, maps, args, num_sms, stream);
+  if (args.D == 256) return launch_t<256>(tmW, maps, args, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

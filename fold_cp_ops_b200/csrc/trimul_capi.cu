@@ -316,14 +316,11 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   if (mask_kind < 0 || mask_kind > 3 || (mask_kind != 0 && mask == nullptr))
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: bad mask_kind %d", mask_kind);
   const int D = geom->d;
-  // CTA pairs share the weight stream, each CTA loading half of a chunk's rows (opt-in through bit 15
-  // of the profiling mask until it has been measured against the single-CTA form)
-  const bool pair = ((debug_skip_bits() >> 15) & 1) && num_sms_current() >= 2;
   CUtensorMap tmW;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(5 * D)};
     const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, static_cast<uint32_t>(pair ? D / 2 : D)};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
     rc = make_tmap(&tmW, w_packed, 2, dims, strides, box);
     if (rc != TRIMUL_OK) return rc;
   }
@@ -395,7 +392,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
   a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 3) << 3;  // bits 10-11: weight-stream probes
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_gated_proj(tmW, maps, a, num_sms_current(), pair, stream);
+  cudaError_t e = trimul::launch_gated_proj(tmW, maps, a, num_sms_current(), stream);
   if (e != cudaSuccess) return cuda_fail(e, "ln_gated_proj launch");
   return TRIMUL_OK;
 }

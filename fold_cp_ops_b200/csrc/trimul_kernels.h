@@ -57,9 +57,8 @@ struct GatedOutMaps {
 };
 
 int gated_proj_smem_bytes(int D);
-// pair = true: CTA pairs share the weight stream (tcgen05 cta_group::2); tmW then has box (64, D/2)
 cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedOutMaps& maps, const GatedProjArgs& args, int num_sms,
-                              bool pair, cudaStream_t stream);
+                              cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // K_B  per-channel N x N x N contraction, back reshard fused in the store
