@@ -60,7 +60,7 @@ def measured_peaks():
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-KB_DRAM_BYTES_PER_PLANE_ELEMENT = 5.907
+KB_DRAM_BYTES_PER_PLANE_ELEMENT = 6.038
 
 
 class ClockSampler:
@@ -467,9 +467,9 @@ def run_ours(args):
         fl_b = 2.0 * B * (D / cp) * N ** 3
         ach = fl_b / (t_b * 1e-3) / 1e12 if t_b > 0 else None
         peak = peaks["bf16_tflops_sustained"]
-        roof = {"bound": "tensor", "kernel": "tri_contract_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+        roof = {"bound": "tensor", "kernel": "tri_contract_pair_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": (ach / peak) if ach else None,
-                # DRAM bytes per launch: ncu measured 5.907 B per plane element (read 4.000 + write 1.907) on
+                # DRAM bytes per launch: ncu measured 6.038 B per plane element (read 4.113 + write 1.925) on
                 # profile_n1024_d256 (profiles/tri_contract_kernel_n1024_d256.md); first-touch traffic only, so it
                 # scales with planes * N^2
                 "traffic": KB_DRAM_BYTES_PER_PLANE_ELEMENT * B * (D / cp) * N * N,
