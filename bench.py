@@ -64,7 +64,7 @@ KB_DRAM_BYTES_PER_PLANE_ELEMENT = 6.038
 
 
 class ClockSampler:
-    """Samples SM clock and clock-event (throttle) reasons every 50 ms through NVML (read-only) from
+    """Samples SM clock and clock-event (throttle) reasons every 10 ms through NVML (read-only) from
     warm-up to the end of the timed work.  The report prefers the samples that fall inside the timed
     steps; when the timed region is too short to hold three samples it widens to everything sampled
     under load (warm-up, timed steps, per-stage passes) and says so in `window`."""
@@ -105,7 +105,7 @@ class ClockSampler:
                     except Exception as e:  # keep what was sampled
                         self.error = repr(e)
                         return
-                    self._stop.wait(0.05)
+                    self._stop.wait(0.01)
 
             self._thread = threading.Thread(target=pump, daemon=True)
             self._thread.start()
@@ -143,8 +143,8 @@ class ClockSampler:
             if r["samples"] >= 3:
                 r["window"] = "timed steps"
                 return r
-        r = self._summary(self.t_load + 0.2, t_stop)
-        r["window"] = "warm-up + timed steps + per-stage passes (timed region shorter than three 50 ms samples)"
+        r = self._summary(self.t_load, t_stop)
+        r["window"] = "warm-up + timed steps + per-stage passes (timed region shorter than three 10 ms samples)"
         return r
 
 
