@@ -19,7 +19,7 @@ LIB_PATH = PKG_DIR / "libtrimul_sm100.so"
 
 SOURCES = ("trimul_capi.cu", "ln_gated_proj.cu", "tri_contract.cu", "tri_contract_pair.cu", "ln_out_proj.cu", "peer_sync.cu",
            "forward_static.cu")
-HEADERS = ("sm100_ptx.cuh", "trimul_common.cuh", "trimul_kernels.h")
+HEADERS = ("sm100_ptx.cuh", "trimul_common.cuh", "trimul_kernels.h", "tri_contract_epilogue.cuh")
 
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",

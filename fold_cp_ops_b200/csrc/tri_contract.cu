@@ -14,8 +14,7 @@
 // of the rank that owns the (i, j) token block: the back all-to-all rides the store, in 128-byte
 // row segments.  Ragged edges and blocks that straddle two owners fall back to 16-byte vector
 // stores from registers.  At cp=1 the only owner is this GPU.
-#include "trimul_common.cuh"
-#include "trimul_kernels.h"
+#include "tri_contract_epilogue.cuh"
 
 namespace trimul {
 
@@ -30,9 +29,6 @@ constexpr int kBBytes = BN * BK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
-constexpr int kOutCols = 64;                       // columns per output store (128-byte rows)
-constexpr int kOutBufBytes = 32 * kOutCols * 2;    // 32 rows x 64 cols bf16 = 4 KB, one per warp and parity
-constexpr int kOutStageBytes = 4 * 2 * kOutBufBytes;
 
 struct SmemCtl {
   uint64_t full[kStages];
@@ -44,7 +40,7 @@ struct SmemCtl {
   volatile uint32_t armed[kStages];  // parity of the phase the producer last armed, 2 = none
 };
 
-constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
+constexpr int kSmemBytes = kStages * kStageBytes + tri::kOutStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
 
 }  // namespace
 
@@ -55,7 +51,7 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // SW128 tiles need 1024-byte alignment
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* out_stage = tiles + kStages * kStageBytes;  // [4 warps][2][32 rows x 128 B], 128-byte swizzle
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(out_stage + kOutStageBytes);
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(out_stage + tri::kOutStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -163,7 +159,6 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t acc = 0, acc_phase = 0, out_par = 0;
-    const long owner_plane_elems = static_cast<long>(p.ni_loc) * p.nj_loc;
     for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int plane = static_cast<int>(t / tiles_per_plane);
       const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
@@ -177,74 +172,9 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       sm100::tcgen05_fence_after_sync();
       const int i0w = ti * BM + quarter * 32;  // first row of this warp's 32-row band
-      const int i = i0w + lane;
-      const bool row_ok = i < p.n_i;
-      const int i_blk = row_ok ? i / p.ni_loc : 0;
-      const int i_l = i - i_blk * p.ni_loc;
-      // the band can go out as TMA stores when it lies inside the matrix and inside one owner's row block
-      const int iw_blk = i0w / p.ni_loc;
-      const bool band_ok = !p.direct_stores && (i0w + 31 < p.n_i) && ((i0w + 31) / p.ni_loc == iw_blk);
-      // destination plane index on the owner: (chan_offset + d_loc) * B + b  == chan_offset*B + plane
-      const long dst_plane = static_cast<long>(p.chan_offset) * p.batch + plane;
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int cc = 0; cc < BN / kOutCols; ++cc) {
-        uint32_t v[kOutCols];
-        {
-          uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
-          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
-          sm100::tmem_ld_32x32b_x32(taddr_row + cc * kOutCols, lo);
-          sm100::tmem_ld_32x32b_x32(taddr_row + cc * kOutCols + 32, hi);
-        }
-        const int j0 = tj * BN + cc * kOutCols;
-        const int jw_blk = j0 / p.nj_loc;
-        const bool fast = band_ok && (j0 + kOutCols - 1 < p.n_j) && ((j0 + kOutCols - 1) / p.nj_loc == jw_blk);
-        uint8_t* buf = out_stage + ((warp - 2) * 2 + (out_par & 1)) * kOutBufBytes;
-        if (fast) {
-          // the store that last used this buffer (two chunks ago) must have finished reading it
-          if (lane == 0) sm100::tma_store_wait_read<1>();
-          __syncwarp();
-        }
-        sm100::tmem_ld_wait();
-        if (fast) {
-#pragma unroll
-          for (int q = 0; q < kOutCols / 8; ++q) {
-            uint4 pk;
-            pk.x = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-            pk.y = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-            pk.z = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-            pk.w = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-            // row = lane, 16-byte chunk q, 128-byte swizzle (what the store descriptor expects)
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) = pk;
-          }
-          sm100::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            sm100::tma_store_3d(&out_maps.map[iw_blk * p.cp1 + jw_blk], buf, j0 - jw_blk * p.nj_loc,
-                                i0w - iw_blk * p.ni_loc, static_cast<int>(dst_plane));
-            sm100::tma_store_commit();
-          }
-          ++out_par;
-        } else if (row_ok && j0 < p.n_j) {
-          // ragged edge or a band that straddles two owners: 16-byte vectors straight from registers
-#pragma unroll
-          for (int q = 0; q < kOutCols / 8; ++q) {
-            const int j = j0 + q * 8;
-            if (j < p.n_j) {  // n_j % 8 == 0: a 16-byte vector never straddles the edge or an owner
-              const int j_blk = j / p.nj_loc;
-              const int j_l = j - j_blk * p.nj_loc;
-              __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.out.ptr[i_blk * p.cp1 + j_blk]);
-              uint4 pk;
-              pk.x = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              pk.y = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              pk.z = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              pk.w = sm100::pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(base + dst_plane * owner_plane_elems + static_cast<long>(i_l) * p.nj_loc +
-                                        j_l) = pk;
-            }
-          }
-        }
-      }
+      tri::store_band(p, out_maps, taddr_row, i0w, tj * BN, plane, out_stage + (warp - 2) * 2 * tri::kOutBufBytes,
+                      out_par, lane);
       sm100::tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
