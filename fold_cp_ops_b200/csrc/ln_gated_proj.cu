@@ -165,6 +165,12 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
   return v;
 }
 
+// Order in which a CTA walks the five column chunks of a tile.  The four gated chunks (a_lo, a_hi,
+// b_lo, b_hi) belong to different owner ranks; CTAs start them at different points of the cycle so
+// that, at any moment, the stores of the whole grid are spread over all owners (and all NVLink
+// directions) instead of everyone sending to the same half of the ranks.  The gate chunk stays last.
+__device__ __forceinline__ int chunk_at(int step, int rot) { return step < 4 ? ((step + rot) & 3) : 4; }
+
 struct TileCoord {
   int b, line, w0;
 };
@@ -197,6 +203,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   const int tiles_per_line = (p.n_walk + BM - 1) / BM;
   const long total_tiles = static_cast<long>(p.batch) * p.n_lines * tiles_per_line;
+  const int rot = (p.debug_skip & 32) ? 0 : static_cast<int>(blockIdx.x & 3);  // see chunk_at; bit 5: same order everywhere
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kWStages; ++s) {
@@ -235,7 +242,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t n_loads = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int c = 0; c < kNumChunks && ok; ++c) {
+        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
+          const int c = chunk_at(ci, rot);
           for (int kb = 0; kb < C::KB; ++kb) {
             if (!sm100::mbar_wait(&ctl->w_empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
               report_timeout(p.status, kKernelGatedProj, 0, c * 16 + kb);
@@ -274,7 +282,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         sm100::tcgen05_fence_after_sync();
         tr.ev(1);
         const uint32_t a_addr = sm100::smem_u32(a_tiles + buf * C::kABytes);
-        for (int c = 0; c < kNumChunks && ok; ++c) {
+        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
+          const int c = chunk_at(ci, rot);
           if (!sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo)) {
             report_timeout(p.status, kKernelGatedProj, 1, -2);
             ok = false;
@@ -325,7 +334,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
         const int dst_x = p.dst_x0 + tc.w0;
         const int dst_y = p.dst_y0 + tc.line;
-        for (int c = 0; c < kNumChunks && ok; ++c) {
+        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
+          const int c = chunk_at(ci, rot);
           const int n_use = (c < 4) ? 1 : 2;
           for (int u = 0; u < n_use; ++u) {
             const uint32_t b = (use + u) & 1, ph = ((use + u) >> 1) & 1;
@@ -476,7 +486,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
-      for (int c = 0; c < kNumChunks; ++c) {
+      for (int ci = 0; ci < kNumChunks; ++ci) {
+        const int c = chunk_at(ci, rot);
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
         // the staging buffer(s) of this chunk must have been forwarded (two uses ago)
         const int n_use = (c < 4) ? 1 : 2;

@@ -389,7 +389,7 @@ int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const v
     rc = make_tmap(&maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TRIMUL_OK) return rc;
   }
-  a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 3) << 3;  // bits 10-11: weight-stream probes
+  a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 7) << 3;  // bits 10-11: weight-stream probes, 12: fixed chunk order
   a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
   cudaError_t e = trimul::launch_gated_proj(tmW, maps, a, num_sms_current(), stream);
