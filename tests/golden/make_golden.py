@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ from the REFERENCE's own oracle.
 
-Run where the reference checkout is importable (``REFERENCE_ROOT``, default ``/root/reference``):
+Run where the reference checkout is importable (its path in ``REFERENCE_ROOT``):
 
     python tests/golden/make_golden.py
 
