@@ -36,23 +36,35 @@ constexpr int kLnWarps = 8;
 constexpr int kEpiWarp0 = 4;
 constexpr int kLnWarp0 = kEpiWarp0 + kEpiWarps;
 constexpr int kThreads = (kLnWarp0 + kLnWarps) * 32;
-constexpr int kNumChunks = 5;            // a_lo, a_hi, b_lo, b_hi, gate
 constexpr int kRowPitch = BM * 2;        // bytes per channel row of the a|b staging tile (128 tokens)
 constexpr int kFwdWarp = 3;              // control warp whose lane 0 forwards staged tiles
 
+// Column chunks of a tile.  A gated chunk always holds 128 channels of a (or b): 128 projection
+// columns followed by the 128 gate columns of the same channels, N = 256 -- the MMA shape that
+// keeps the tensor core off the shared-memory bandwidth limit (a 128 x 128 x 16 MMA reads as many
+// operand bytes as it has clocks for).  D = 256: a_lo, a_hi, b_lo, b_hi, gate (N = 256);
+// D = 128: a, b, gate (N = 128).
 template <int D>
 struct Cfg {
-  static constexpr int CH = D / 2;              // channels per gated chunk
+  static constexpr int CH = 128;                // channels per gated chunk
+  static constexpr int kChunkN = 2 * CH;        // columns of a gated chunk (also the accumulator stride in TMEM)
+  static constexpr int kGated = 2 * D / CH;     // gated chunks per tile
+  static constexpr int kPerHalf = kGated / 2;   // gated chunks of a (and of b)
+  static constexpr int kNumChunks = kGated + 1; // + the output-gate chunk (N = D)
   static constexpr int KB = D / 64;             // 64-wide K blocks
   static constexpr int kABytes = BM * D * 2;    // one operand tile
   static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
-  static constexpr int kWStageBytes = D * 128;  // D weight rows x 64 k
-  static constexpr int kWStages = (D == 256) ? 3 : 4;
+  static constexpr int kWBoxRows = D;           // rows one weight TMA box brings (the packed matrix has 5 D rows)
+  static constexpr int kWStageBytes = kChunkN * 128;  // one stage: up to 256 weight rows x 64 k
+  static constexpr int kWStages = 3;
   static constexpr int kABufs = (D == 256) ? 1 : 2;
-  static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
-  static constexpr int kStageBuf = CH * kRowPitch;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or half of the gate tile
+  static constexpr int kTmemCols = 512;
+  static constexpr int kStageBuf = CH * kRowPitch;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or two gate boxes
   static constexpr int kGateBoxBytes = BM * 128;     // gate box: 128 tokens x 64 channels, 128-byte swizzle
-  static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes + 2 * kStageBuf;
+  static constexpr int kStBufs = 2;                  // staging buffers (two to four; more did not pay at D = 128)
+  static constexpr int kBoxesPerBuf = kStageBuf / kGateBoxBytes;  // gate boxes one buffer holds
+  static constexpr int kGateUses = (D / 64) / kBoxesPerBuf;       // staging buffers the gate chunk fills
+  static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes + kStBufs * kStageBuf;
 };
 
 template <int D>
@@ -63,8 +75,8 @@ struct SmemCtl {
   uint64_t x_empty[2];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t st_full[2];   // staging buffer written by all sixteen epilogue warps
-  uint64_t st_free[2];   // ... and read completely by the forwarder's bulk stores
+  uint64_t st_full[4];   // staging buffer written by all sixteen epilogue warps (kStBufs of them are used)
+  uint64_t st_free[4];   // ... and read completely by the forwarder's bulk stores
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kWStages];
@@ -169,7 +181,10 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
 // b_lo, b_hi) belong to different owner ranks; CTAs start them at different points of the cycle so
 // that, at any moment, the stores of the whole grid are spread over all owners (and all NVLink
 // directions) instead of everyone sending to the same half of the ranks.  The gate chunk stays last.
-__device__ __forceinline__ int chunk_at(int step, int rot) { return step < 4 ? ((step + rot) & 3) : 4; }
+template <int GATED>
+__device__ __forceinline__ int chunk_at(int step, int rot) {
+  return step < GATED ? ((step + rot) & (GATED - 1)) : GATED;
+}
 
 struct TileCoord {
   int b, line, w0;
@@ -195,7 +210,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = tiles;                              // kABufs x kABytes
   uint8_t* w_tiles = tiles + C::kABufs * C::kABytes;     // kWStages x kWStageBytes
-  uint8_t* st_tiles = w_tiles + C::kWStages * C::kWStageBytes;  // 2 x kStageBuf
+  uint8_t* st_tiles = w_tiles + C::kWStages * C::kWStageBytes;  // kStBufs x kStageBuf
   SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -216,8 +231,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sm100::mbar_init(&ctl->x_empty[a], 1);     // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_full[a], 1);   // tcgen05.commit
       sm100::mbar_init(&ctl->tmem_empty[a], kEpiWarps);  // one arrive per epilogue warp
-      sm100::mbar_init(&ctl->st_full[a], kEpiWarps);     // one arrive per epilogue warp
-      sm100::mbar_init(&ctl->st_free[a], 1);             // the forwarder
+    }
+    for (int b = 0; b < C::kStBufs; ++b) {
+      sm100::mbar_init(&ctl->st_full[b], kEpiWarps);     // one arrive per epilogue warp
+      sm100::mbar_init(&ctl->st_free[b], 1);             // the forwarder
     }
     ctl->abort_flag = 0;
     sm100::mbar_init_fence();
@@ -242,8 +259,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t n_loads = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
-          const int c = chunk_at(ci, rot);
+        for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
+          const int c = chunk_at<C::kGated>(ci, rot);
           for (int kb = 0; kb < C::KB; ++kb) {
             if (!sm100::mbar_wait(&ctl->w_empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
               report_timeout(p.status, kKernelGatedProj, 0, c * 16 + kb);
@@ -258,9 +275,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             if (skip_load) {
               sm100::mbar_arrive(&ctl->w_full[ps.stage]);
             } else {
+              // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunk the last D rows
+              const int rows = c < C::kGated ? C::kChunkN : D;
               ctl->armed[ps.stage] = ps.phase;
-              sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], C::kWStageBytes);
-              sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes, &tmW, &ctl->w_full[ps.stage], kb * 64, c * D);
+              sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], rows * 128);
+              for (int r0 = 0; r0 < rows; r0 += C::kWBoxRows) {
+                sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes + r0 * 128, &tmW, &ctl->w_full[ps.stage], kb * 64,
+                                   c * C::kChunkN + r0);
+              }
             }
             ps.advance(C::kWStages);
           }
@@ -268,7 +290,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- UMMA issuer
-      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D);
+      constexpr uint32_t idesc_gated = sm100::umma_idesc_bf16_f32(BM, C::kChunkN);
+      constexpr uint32_t idesc_gate = sm100::umma_idesc_bf16_f32(BM, D);
       Tracer tr;
       tr.init(0);
       PipeState ps{0, 0};
@@ -282,8 +305,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         sm100::tcgen05_fence_after_sync();
         tr.ev(1);
         const uint32_t a_addr = sm100::smem_u32(a_tiles + buf * C::kABytes);
-        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
-          const int c = chunk_at(ci, rot);
+        for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
+          const int c = chunk_at<C::kGated>(ci, rot);
           if (!sm100::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, tmo)) {
             report_timeout(p.status, kKernelGatedProj, 1, -2);
             ok = false;
@@ -291,7 +314,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           sm100::tcgen05_fence_after_sync();
           tr.ev(2);
-          const uint32_t d_tmem = tmem_base + acc * D;
+          const uint32_t d_tmem = tmem_base + acc * C::kChunkN;
+          const uint32_t idesc = c < C::kGated ? idesc_gated : idesc_gate;
           for (int kb = 0; kb < C::KB; ++kb) {
             if (!sm100::mbar_wait(&ctl->w_full[ps.stage], ps.phase, abort_flag, tmo)) {
               report_timeout(p.status, kKernelGatedProj, 1, c * 16 + kb);
@@ -325,50 +349,54 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
     } else if (warp == kFwdWarp && lane == 0) {
       // ---------------------------------------------------------- forwarder (TMA stores of staged tiles)
-      // Six buffer uses per tile: four a|b chunks (one buffer each) and the gate tile (both buffers).
+      // Six buffer uses per tile: four a|b chunks (one buffer each) and the gate tile (two buffers).
+      // Use u lives in buffer u % kStBufs, phase (u / kStBufs) & 1; every use is one bulk group.  A
+      // buffer is handed back when its group has been read; with more than two buffers the forwarder
+      // waits only for the group kStBufs - 2 behind the newest, so it never stalls on its own last
+      // stores.
+      constexpr uint32_t NB = C::kStBufs;
       const int d_loc_mask = (1 << p.d_loc_log2) - 1;
       const int d_loc_n = 1 << p.d_loc_log2;
-      uint32_t use = 0;  // running count of buffer uses; buffer = use & 1, phase = (use >> 1) & 1
+      uint32_t use = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
         const int dst_x = p.dst_x0 + tc.w0;
         const int dst_y = p.dst_y0 + tc.line;
-        for (int ci = 0; ci < kNumChunks && ok; ++ci) {
-          const int c = chunk_at(ci, rot);
-          const int n_use = (c < 4) ? 1 : 2;
-          for (int u = 0; u < n_use; ++u) {
-            const uint32_t b = (use + u) & 1, ph = ((use + u) >> 1) & 1;
+        for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
+          const int c = chunk_at<C::kGated>(ci, rot);
+          const int n_use = (c < C::kGated) ? 1 : C::kGateUses;
+          for (int u = 0; u < n_use && ok; ++u, ++use) {
+            const uint32_t b = use % NB, ph = (use / NB) & 1;
             if (!sm100::mbar_wait(&ctl->st_full[b], ph, abort_flag, tmo)) {
               report_timeout(p.status, kKernelGatedProj, 4, c);
               ok = false;
               break;
             }
-          }
-          if (!ok) break;
-          if (c < 4) {
-            const uint8_t* src = st_tiles + (use & 1) * C::kStageBuf;
-            const int h = c >> 1;
-            if (!(p.debug_skip & 1)) {
+            const uint8_t* src = st_tiles + b * C::kStageBuf;
+            if (c < C::kGated) {
+              const int h = c / C::kPerHalf;   // 0: a, 1: b
+              if (!(p.debug_skip & 1)) {
 #pragma unroll 1
-              for (int k = 0; k < C::CH / 16; ++k) {
-                const int d = (c & 1) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
-                sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], src + k * 16 * kRowPitch, dst_x, dst_y, tc.b,
-                                    h * d_loc_n + (d & d_loc_mask));
+                for (int k = 0; k < C::CH / 16; ++k) {
+                  const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
+                  sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], src + k * 16 * kRowPitch, dst_x, dst_y, tc.b,
+                                      h * d_loc_n + (d & d_loc_mask));
+                }
+              }
+            } else if (!(p.debug_skip & 2)) {
+              const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
+              const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
+#pragma unroll 1
+              for (int j = 0; j < C::kBoxesPerBuf; ++j) {
+                const int jb = u * C::kBoxesPerBuf + j;  // gate box: channels [64 jb, 64 jb + 64)
+                sm100::tma_store_4d(&om.gate, src + j * C::kGateBoxBytes, jb * 64, cw, cl, tc.b);
               }
             }
-          } else if (!(p.debug_skip & 2)) {
-            const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
-            const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
-#pragma unroll 1
-            for (int jb = 0; jb < D / 64; ++jb) {
-              sm100::tma_store_4d(&om.gate, st_tiles + jb * C::kGateBoxBytes, jb * 64, cw, cl, tc.b);
-            }
+            sm100::tma_store_commit();
+            sm100::tma_store_wait_read<NB - 2>();  // every group but the newest NB - 2 has read its buffer
+            if (use + 2 >= NB) sm100::mbar_arrive(&ctl->st_free[(use + 2 - NB) % NB]);
           }
-          sm100::tma_store_commit();
-          sm100::tma_store_wait_read<0>();  // the bulk stores have read the staging buffer(s)
-          for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_free[(use + u) & 1]);
-          use += n_use;
         }
       }
       sm100::tma_store_wait_all<0>();  // every bulk store has been performed before the CTA retires
@@ -486,13 +514,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
-      for (int ci = 0; ci < kNumChunks; ++ci) {
-        const int c = chunk_at(ci, rot);
+      for (int ci = 0; ci < C::kNumChunks; ++ci) {
+        const int c = chunk_at<C::kGated>(ci, rot);
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
         // the staging buffer(s) of this chunk must have been forwarded (two uses ago)
-        const int n_use = (c < 4) ? 1 : 2;
+        constexpr uint32_t NB = C::kStBufs;
+        const int n_use = (c < C::kGated) ? 1 : C::kGateUses;
         for (int u = 0; u < n_use; ++u) {
-          const uint32_t b = (use + u) & 1, ph = ((use + u) >> 1) & 1;
+          const uint32_t b = (use + u) % NB, ph = ((use + u) / NB) & 1;
           ok = ok && sm100::mbar_wait(&ctl->st_free[b], ph ^ 1, abort_flag, tmo);
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -502,15 +531,15 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
         sm100::tcgen05_fence_after_sync();
         if (ew == 0 && lane == 0) tr.ev(4);
-        const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
-        if (c < 4) {
+        const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kChunkN;
+        if (c < C::kGated) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
           constexpr int CW = C::CH / 4;   // channels of the chunk this warp handles
           constexpr int NS = CW / 16;     // in 16-channel sub-groups
           const int colw = part * CW;
-          const float* bias_p0 = p.bias + c * D + colw;
+          const float* bias_p0 = p.bias + c * C::kChunkN + colw;
           const bool has_mask = p.mask_kind != 0;
-          uint8_t* rows = st_tiles + (use & 1) * C::kStageBuf + colw * kRowPitch + r * 2;
+          uint8_t* rows = st_tiles + (use % NB) * C::kStageBuf + colw * kRowPitch + r * 2;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
             uint32_t pv[16], gv[16];
@@ -528,7 +557,9 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           constexpr int NS = GW / 16;
           const int colw = part * GW;
           const float* bias_g0 = p.bias + 4 * D + colw;
-          uint8_t* box = st_tiles + (colw >> 6) * C::kGateBoxBytes;
+          const int jb = colw >> 6;  // gate box of this warp's columns; boxes fill the chunk's two buffers in order
+          uint8_t* box = st_tiles + ((use + jb / C::kBoxesPerBuf) % NB) * C::kStageBuf +
+                         (jb % C::kBoxesPerBuf) * C::kGateBoxBytes;
           const int slot_base = (colw & 63) >> 3;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
@@ -545,7 +576,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         __syncwarp();
         if (lane == 0) {
           sm100::mbar_arrive(&ctl->tmem_empty[acc]);
-          for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_full[(use + u) & 1]);
+          for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_full[(use + u) % NB]);
         }
         use += n_use;
         if (ew == 0 && lane == 0) tr.ev(5);

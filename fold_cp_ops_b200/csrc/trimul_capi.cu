@@ -171,18 +171,21 @@ __global__ void pack_weights_kernel(int d, const __nv_bfloat16* p_in, const __nv
                                     const __nv_bfloat16* g_out, const float* p_in_b, const float* g_in_b,
                                     const float* g_out_b, __nv_bfloat16* w_packed, float* bias_packed) {
   const int row = blockIdx.x;  // packed row 0 .. 5d-1
-  const int ch = d / 2;
-  const int chunk = row / d;
-  const int rr = row - chunk * d;
+  // rows [0, 4d): gated chunks of 256 rows = 128 projection rows followed by the 128 gate rows of the
+  // same channels; chunk c covers rows [128 c, 128 c + 128) of the (2d, d) matrices (a first, then b).
+  // rows [4d, 5d): the output gate.
   const __nv_bfloat16* src;
   float bias;
-  if (chunk < 4) {
-    const bool is_gate = rr >= ch;
-    const int src_row = chunk * ch + (is_gate ? rr - ch : rr);  // row of the (2d, d) matrix
+  if (row < 4 * d) {
+    const int c = row / 256;
+    const int rr = row - c * 256;
+    const bool is_gate = rr >= 128;
+    const int src_row = c * 128 + (rr & 127);
     src = (is_gate ? g_in : p_in) + static_cast<long>(src_row) * d;
     const float* b = is_gate ? g_in_b : p_in_b;
     bias = b ? b[src_row] : 0.0f;
   } else {
+    const int rr = row - 4 * d;
     src = g_out + static_cast<long>(rr) * d;
     bias = g_out_b ? g_out_b[rr] : 0.0f;
   }

@@ -120,9 +120,9 @@ int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out);
 const char* trimul_sm100_last_error(void);
 
 /* Pack the input-side weights once at construction: rows of p_in / g_in / g_out (each row-major
- * (out, in), bf16) are regrouped into five d-row chunks [a_lo|a_hi|b_lo|b_hi: d/2 projection rows
- * then the d/2 matching gate rows][g_out: d rows]; biases (fp32, any may be NULL) are packed the
- * same way.  Every packed row and bias is scaled by 1/2 (exact), which lets the kernel evaluate
+ * (out, in), bf16) are regrouped into 4d/256 gated chunks of 256 rows (128 projection rows of a --
+ * then of b -- followed by the 128 matching gate rows) and the d rows of g_out; biases (fp32, any may
+ * be NULL) are packed the same way.  Every packed row and bias is scaled by 1/2 (exact), which lets the kernel evaluate
  * p * sigmoid(g) as (p/2) * tanh(g/2) + p/2.  w_packed: (5d, d) bf16; bias_packed: (5d) fp32.
  * Replaces `interleave_dual_weights` (fold_cp_ops/kernels/dual_gated_gemm.py:958). */
 int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
