@@ -11,8 +11,10 @@
 // Persistent CTA, 128-token tiles.  Eight LayerNorm warps pull token rows from HBM into
 // registers, normalise them there (two-pass fp32 statistics), and write the bf16 operand tile into
 // shared memory in the K-major 128-byte-swizzle layout once the tensor core has released it;
-// weights stream through a TMA ring (they live in L2); one thread issues tcgen05.mma for five
-// N=D column chunks per tile into two TMEM accumulators; sixteen epilogue warps (four per TMEM
+// weights stream through a TMA ring (they live in L2); one thread issues tcgen05.mma for the
+// tile's column chunks (128 gated channels = 256 columns each, then the output gate) into two
+// TMEM accumulators, every CTA starting the gated chunks at a different point so that the grid's
+// stores are spread over all owner ranks; sixteen epilogue warps (four per TMEM
 // lane quarter) apply bias / gate / mask and write bf16 into a CTA-wide staging tile
 // [channel][128 tokens] (double-buffered); when all sixteen have arrived, one forwarding thread
 // sends the tile as TMA stores of 16 channels x 128 tokens -- 256-byte rows -- into the
