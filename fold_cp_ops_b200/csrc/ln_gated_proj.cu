@@ -516,6 +516,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
         }
       }
+      // a warp whose 32 tokens all carry mask 1 (the common case) skips the multiply: x * 1 is exact
+      const bool warp_has_mask = p.mask_kind != 0 && !__all_sync(0xffffffffu, mval == 1.0f);
       for (int ci = 0; ci < C::kNumChunks; ++ci) {
         const int c = chunk_at<C::kGated>(ci, rot);
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
@@ -540,7 +542,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           constexpr int NS = CW / 16;     // in 16-channel sub-groups
           const int colw = part * CW;
           const float* bias_p0 = p.bias + c * C::kChunkN + colw;
-          const bool has_mask = p.mask_kind != 0;
+          const bool has_mask = warp_has_mask;
           uint8_t* rows = st_tiles + (use % NB) * C::kStageBuf + colw * kRowPitch + r * 2;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
