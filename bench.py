@@ -44,7 +44,7 @@ WORKLOADS = {
     "profile_n1024_d256": (1, 1024, 1024, 256),   # small case for ncu captures (inputs > L2, < 2 GB on device)
     "profile_n2048_d128": (1, 2048, 2048, 128),
 }
-CPU_SAMPLE_N = 384  # token extent of the bounded CPU sample (same D, same distributions)
+CPU_SAMPLE_N = 768  # token extent of the bounded CPU sample (same D, same distributions)
 
 
 def flops(B, N, D):
