@@ -367,18 +367,19 @@ def run_ours(args):
         eng = next(reversed(wf._ENGINE_CACHE.values())) if wf._ENGINE_CACHE else None
     else:
         eng = next(iter(trimul._engines.values()))
+    fwd_stats = None
     if eng is not None and not args.kernels_only:
-        eng.stage_log = True
-        import contextlib
-        import io
-        acc = {}
-        with contextlib.redirect_stdout(io.StringIO()):
-            for _ in range(3):
-                step_resident()
-                for k, v in eng.last_stage_ms.items():
-                    acc.setdefault(k, []).append(v)
-        eng.stage_log = False
-        stage_ms = {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
+        # kernel-only CUDA-event windows (the flag kernels are outside them) and the device timeline
+        eng.collect_stats = True
+        runs = []
+        for _ in range(3):
+            step_resident()
+            runs.append(eng.last_forward_stats())
+        eng.collect_stats = False
+        med = lambda vals: sorted(vals)[len(vals) // 2]
+        stage_ms = {k: med([r["stage_ms"][k] for r in runs]) for k in runs[0]["stage_ms"]}
+        fwd_stats = runs[-1]
+        fwd_stats["wait_ms"] = {k: med([r["wait_ms"][k] or 0.0 for r in runs]) for k in runs[0]["wait_ms"]}
     clocks = sampler.stop() if sampler else None
     # ---- e2e: pinned host -> device, forward, device -> pinned host, every step -----------------
     # Serial form first (copy in, forward, copy out on one stream: the latency of one request), then the

@@ -38,6 +38,11 @@ EXPORTED_SYMBOLS = (
     "trimul_sm100_ln_out_proj",
     "trimul_sm100_forward",
     "trimul_sm100_forward_static",
+    "trimul_sm100_plan_create",
+    "trimul_sm100_plan_ln_gated_proj",
+    "trimul_sm100_plan_tri_contract",
+    "trimul_sm100_plan_ln_out_proj",
+    "trimul_sm100_plan_destroy",
     "trimul_sm100_peer_signal",
     "trimul_sm100_peer_wait",
 )
@@ -51,6 +56,28 @@ class Caps(C.Structure):
 class Geom(C.Structure):
     _fields_ = [("batch", C.c_int32), ("n", C.c_int32), ("d", C.c_int32), ("cp0", C.c_int32),
                 ("cp1", C.c_int32), ("rank", C.c_int32), ("direction", C.c_int32), ("eps", C.c_float)]
+
+
+class Tuning(C.Structure):
+    _fields_ = [("contract_form", C.c_int32), ("front_fixed_order", C.c_int32), ("reserved", C.c_int32 * 6)]
+
+
+CONTRACT_DEFAULT, CONTRACT_SINGLE, CONTRACT_PAIR = 0, 1, 2
+TIMELINE_SLOTS = 16
+TL_FRONT_START, TL_FRONT_FIRST_STORE, TL_FRONT_LAST_STORE = 0, 1, 2
+TL_CONTRACT_START, TL_CONTRACT_LAST_STORE, TL_OUT_START, TL_OUT_END, TL_WAIT_BASE = 3, 4, 5, 6, 8
+
+
+class Status(C.Structure):
+    _fields_ = [("code", C.c_int32), ("kernel", C.c_int32), ("block", C.c_int32), ("role", C.c_int32),
+                ("detail", C.c_int32), ("pad", C.c_int32 * 3)]
+
+
+class PlanDesc(C.Structure):
+    _fields_ = [("geom", Geom), ("tuning", Tuning), ("ln_in_w", C.c_void_p), ("ln_in_b", C.c_void_p),
+                ("w_packed", C.c_void_p), ("bias_packed", C.c_void_p), ("w_fold", C.c_void_p), ("cd", C.c_void_p),
+                ("ab_peers", C.c_void_p * MAX_PEERS), ("tri_peers", C.c_void_p * MAX_PEERS), ("gate", C.c_void_p),
+                ("status", C.c_void_p), ("timeline", C.c_void_p), ("timeout_ns", C.c_uint64)]
 
 
 class Workspace(C.Structure):
@@ -77,6 +104,18 @@ def library_path() -> Path:
     return Path(override) if override else _PKG_DIR / LIB_NAME
 
 
+def override_is_default() -> bool:
+    return not os.environ.get("CPO_TRIMUL_LIB")
+
+
+def _sources_newer_than(path: Path) -> bool:
+    """True when a kernel source or the public header was modified after the library was built."""
+    t = path.stat().st_mtime
+    deps = list((_PKG_DIR / "csrc").glob("*.cu*")) + list((_PKG_DIR / "csrc").glob("*.h")) + \
+        [_PKG_DIR.parent / "include" / "trimul_sm100.h"]
+    return any(d.exists() and d.stat().st_mtime > t for d in deps)
+
+
 def load():
     """Load the shared library once; raise :class:`TrimulLibraryError` if it is not there."""
     global _lib
@@ -91,10 +130,19 @@ def load():
                 f"{path} not found. Build it with `python -m fold_cp_ops_b200.build` (needs nvcc); "
                 "there is no PyTorch or CPU fallback for the TriMul kernels."
             )
+        if override_is_default() and _sources_newer_than(path):
+            raise TrimulLibraryError(
+                f"{path} is older than the CUDA sources next to it; rebuild it with "
+                "`python -m fold_cp_ops_b200.build` (a stale library is never loaded silently).")
         try:
             lib = C.CDLL(str(path))
         except OSError as exc:  # pragma: no cover - depends on the host
             raise TrimulLibraryError(f"cannot load {path}: {exc}") from exc
+        missing = [name for name in EXPORTED_SYMBOLS if not hasattr(lib, name)]
+        if missing:
+            raise TrimulLibraryError(
+                f"{path} was built from older sources: it does not export {missing}. Rebuild it with "
+                "`python -m fold_cp_ops_b200.build`.")
         vp, i32, u64, f32p = C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p
         lib.trimul_sm100_last_error.restype = C.c_char_p
         lib.trimul_sm100_last_error.argtypes = []
@@ -103,9 +151,15 @@ def load():
         lib.trimul_sm100_reshard_plan.argtypes = [C.POINTER(Geom), C.POINTER(ReshardPlan)]
         lib.trimul_sm100_reshard_plan.restype = C.c_int
         lib.trimul_sm100_pack_weights.argtypes = [i32, vp, vp, vp, f32p, f32p, f32p, vp, f32p, vp]
-        lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p,
+        lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), C.POINTER(Tuning), vp, vp, i32, f32p, f32p, vp, f32p,
                                                    C.POINTER(vp), vp, vp, u64, vp]
-        lib.trimul_sm100_tri_contract.argtypes = [C.POINTER(Geom), vp, C.POINTER(vp), vp, u64, vp]
+        lib.trimul_sm100_tri_contract.argtypes = [C.POINTER(Geom), C.POINTER(Tuning), vp, C.POINTER(vp), vp, u64, vp]
+        lib.trimul_sm100_plan_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(vp)]
+        lib.trimul_sm100_plan_ln_gated_proj.argtypes = [vp, vp, vp, i32, vp]
+        lib.trimul_sm100_plan_tri_contract.argtypes = [vp, vp]
+        lib.trimul_sm100_plan_ln_out_proj.argtypes = [vp, vp, vp]
+        lib.trimul_sm100_plan_destroy.argtypes = [vp]
+        lib.trimul_sm100_plan_destroy.restype = None
         lib.trimul_sm100_pack_out_weights.argtypes = [i32, vp, f32p, f32p, f32p, vp, f32p, vp]
         lib.trimul_sm100_ln_out_proj.argtypes = [C.POINTER(Geom), vp, vp, vp, f32p, vp, vp, u64, vp]
         lib.trimul_sm100_forward.argtypes = [C.POINTER(Geom), vp, vp, i32, f32p, f32p, vp, f32p, vp, f32p,
@@ -114,11 +168,13 @@ def load():
                                                     vp, vp, u64, vp]
         lib.trimul_sm100_forward_static.restype = C.c_int
         lib.trimul_sm100_peer_signal.argtypes = [C.POINTER(vp), i32, i32, vp]
-        lib.trimul_sm100_peer_wait.argtypes = [vp, i32, u64, vp, u64, vp]
+        lib.trimul_sm100_peer_wait.argtypes = [vp, i32, u64, vp, vp, u64, vp]
         for name in ("trimul_sm100_query", "trimul_sm100_workspace", "trimul_sm100_pack_weights",
                      "trimul_sm100_pack_out_weights",
                      "trimul_sm100_ln_gated_proj", "trimul_sm100_tri_contract", "trimul_sm100_ln_out_proj",
-                     "trimul_sm100_forward", "trimul_sm100_peer_signal", "trimul_sm100_peer_wait"):
+                     "trimul_sm100_forward", "trimul_sm100_peer_signal", "trimul_sm100_peer_wait",
+                     "trimul_sm100_plan_create", "trimul_sm100_plan_ln_gated_proj", "trimul_sm100_plan_tri_contract",
+                     "trimul_sm100_plan_ln_out_proj"):
             getattr(lib, name).restype = C.c_int
         _lib = lib
         return lib

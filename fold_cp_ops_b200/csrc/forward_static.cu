@@ -21,17 +21,21 @@
 //     element it later reads (all operand planes, the whole gate, the whole contraction result),
 //     so nothing has to be cleared between calls and nothing is.
 //   * the first call on each device resolves the array's device address (cudaGetSymbolAddress,
-//     with that device current).  Make that first call outside any stream capture; later calls
-//     on the same device reuse the cached address.
+//     with that device current -- the device that owns `stream` must be the current device).  Make
+//     that first call outside any stream capture; later calls on the same device reuse the cached
+//     address.  The cache lives as long as the process: after a cudaDeviceReset the cached address
+//     is stale and this entry point must not be used again in that process.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+
+#include <atomic>
 
 #include "../../include/trimul_sm100.h"
 
 namespace {
 
-constexpr size_t kTrimulStaticScratchBytes = 32ull << 20;
+constexpr size_t kTrimulStaticScratchBytes = TRIMUL_STATIC_SCRATCH_BYTES;  // the capacity the header promises
 
 // File-scope device array.  In host code this NAME is only a handle for the runtime's symbol
 // table, not a device pointer: it must never be passed to a kernel or used in pointer arithmetic.
@@ -39,7 +43,9 @@ constexpr size_t kTrimulStaticScratchBytes = 32ull << 20;
 static __device__ __align__(256) unsigned char g_trimul_static_scratch[kTrimulStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices];  // per-device address of the array, resolved on first use
+// Per-device address of the array, resolved on first use.  Atomic slots: host threads may race on
+// their first calls; every racer resolves the same address, so the last store wins harmlessly.
+std::atomic<void*> g_scratch_addr[kMaxDevices];
 
 // Device address of the scratch array on the CURRENT device (resolved once per device).
 int scratch_base(unsigned char** out, char* msg, size_t msg_len) {
@@ -50,17 +56,17 @@ int scratch_base(unsigned char** out, char* msg, size_t msg_len) {
              cudaGetErrorString(e));
     return TRIMUL_ERR_CUDA;
   }
-  if (g_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     e = cudaGetSymbolAddress(&ptr, g_trimul_static_scratch);
     if (e != cudaSuccess || ptr == nullptr) {
       snprintf(msg, msg_len, "forward_static: cudaGetSymbolAddress failed on device %d (%s)", dev,
                cudaGetErrorString(e));
       return TRIMUL_ERR_CUDA;
     }
-    g_scratch_addr[dev] = ptr;
+    g_scratch_addr[dev].store(ptr, std::memory_order_release);
   }
-  *out = static_cast<unsigned char*>(g_scratch_addr[dev]);
+  *out = static_cast<unsigned char*>(ptr);
   return TRIMUL_OK;
 }
 

@@ -14,14 +14,18 @@
 // weights stream through a TMA ring (they live in L2); one thread issues tcgen05.mma for the
 // tile's column chunks (128 gated channels = 256 columns each, then the output gate) into two
 // TMEM accumulators, every CTA starting the gated chunks at a different point so that the grid's
-// stores are spread over all owner ranks; sixteen epilogue warps (four per TMEM
-// lane quarter) apply bias / gate / mask and write bf16 into a CTA-wide staging tile
-// [channel][128 tokens] (double-buffered); when all sixteen have arrived, one forwarding thread
-// sends the tile as TMA stores of 16 channels x 128 tokens -- 256-byte rows -- into the
-// channel-major operand plane of the rank that owns the channels (front all-to-all fused in the
-// store; at cp=1 that rank is this GPU).  The output gate leaves the same way, token-major.
-// No thread issues a global store: per-thread 16-byte stores cost this kernel 40 % of its time,
-// and rows shorter than 128 bytes reach half of the HBM / NVLink write rate.
+// stores are spread over all owner ranks; sixteen epilogue warps (four per TMEM lane quarter)
+// apply bias / gate / mask.  The accumulator is token-per-lane but the operand planes are
+// channel-major, so the gated chunks are read in the 16x256b fragment layout (tcgen05.ld), packed
+// two channels to a bf16x2 register, and written with stmatrix.trans: one warp instruction stores
+// 8 channels x 32 tokens as 16-byte rows of eight consecutive tokens -- the transpose costs no
+// instruction of its own.  The CTA-wide staging tile is [token half][channel][64 tokens] with the
+// 128-byte swizzle (double-buffered); when all sixteen warps have arrived, one forwarding thread
+// sends it as TMA stores of 16 channels x 64 tokens into the channel-major operand plane of the
+// rank that owns the channels (front all-to-all fused in the store; at cp=1 that rank is this GPU).
+// The output gate leaves the same way, token-major.  No thread issues a global store: per-thread
+// 16-byte stores cost this kernel 40 % of its time, and rows shorter than 128 bytes reach half of
+// the HBM / NVLink write rate.
 #include "trimul_common.cuh"
 #include "trimul_kernels.h"
 
@@ -38,7 +42,7 @@ constexpr int kLnWarps = 8;
 constexpr int kEpiWarp0 = 4;
 constexpr int kLnWarp0 = kEpiWarp0 + kEpiWarps;
 constexpr int kThreads = (kLnWarp0 + kLnWarps) * 32;
-constexpr int kRowPitch = BM * 2;        // bytes per channel row of the a|b staging tile (128 tokens)
+constexpr int kHalfTokens = 64;          // tokens per staged row: 128 bytes, the swizzle span
 constexpr int kFwdWarp = 3;              // control warp whose lane 0 forwards staged tiles
 
 // Column chunks of a tile.  A gated chunk always holds 128 channels of a (or b): 128 projection
@@ -61,7 +65,8 @@ struct Cfg {
   static constexpr int kWStages = 3;
   static constexpr int kABufs = (D == 256) ? 1 : 2;
   static constexpr int kTmemCols = 512;
-  static constexpr int kStageBuf = CH * kRowPitch;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or two gate boxes
+  static constexpr int kHalfBytes = CH * 128;        // one token half of a staged a|b chunk: CH channel rows of 64 tokens
+  static constexpr int kStageBuf = 2 * kHalfBytes;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or two gate boxes
   static constexpr int kGateBoxBytes = BM * 128;     // gate box: 128 tokens x 64 channels, 128-byte swizzle
   static constexpr int kStBufs = 2;                  // staging buffers (two to four; more did not pay at D = 128)
   static constexpr int kBoxesPerBuf = kStageBuf / kGateBoxBytes;  // gate boxes one buffer holds
@@ -89,59 +94,59 @@ constexpr int smem_bytes() {
   return Cfg<D>::kTileBytes + 1024 + static_cast<int>(sizeof(SmemCtl<D>)) + 64;
 }
 
-// Optional device timeline of CTA 0 (profiling aid): (globaltimer << 8 | event id) records.  Each
-// tracing thread owns a private region (role * cap) and a private counter, so an event costs one
-// fire-and-forget store.
-__device__ unsigned long long* g_trace_buf = nullptr;
-__device__ unsigned int g_trace_cap = 0;  // records per role
-struct Tracer {
-  unsigned long long* base;
-  unsigned int n, cap;
-  __device__ __forceinline__ void init(int role) {
-    base = (g_trace_buf != nullptr && blockIdx.x == 0) ? g_trace_buf + static_cast<size_t>(role) * g_trace_cap : nullptr;
-    n = 0;
-    cap = g_trace_cap;
-  }
-  __device__ __forceinline__ void ev(int id) {
-    if (base != nullptr && n < cap) base[n++] = (sm100::globaltimer_ns() << 8) | static_cast<unsigned long long>(id & 0xff);
-  }
-};
-
 __device__ __forceinline__ float tanh_approx(float x) {
   float t;
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
   return t;
 }
 
-// Sixteen channels of a gated chunk for this thread's token: pv = p/2 and gv = g/2 accumulators.
-// The bf16 results go to the staging tile as tile[channel][token] (256-byte rows, the dense layout
-// of a (128 token, 16 channel) TMA box); the 2-byte stores of a warp are conflict-free.
+// Two neighbouring channels of one token of a gated chunk: (pa, pb) = p/2 and (ga, gb) = g/2
+// accumulators; returns the pair as bf16x2 (even channel in the low half).
 template <bool HAS_BIAS, bool HAS_MASK>
-__device__ __forceinline__ void gate_to_stage16(const uint32_t (&pv)[16], const uint32_t (&gv)[16], const float* bias_p,
-                                                const float* bias_g, float mval, uint8_t* stage_rows) {
-#pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    float pr = __uint_as_float(pv[e]);
-    float ga = __uint_as_float(gv[e]);
-    if (HAS_BIAS) {
-      pr += __ldg(bias_p + e);
-      ga += __ldg(bias_g + e);
-    }
-    float val = fmaf(pr, tanh_approx(ga), pr);
-    if (HAS_MASK) val *= mval;
-    *reinterpret_cast<__nv_bfloat16*>(stage_rows + e * kRowPitch) = __float2bfloat16_rn(val);
+__device__ __forceinline__ uint32_t gate_pair(uint32_t pa, uint32_t pb, uint32_t ga, uint32_t gb, float2 bias_p,
+                                              float2 bias_g, float mval) {
+  float p0 = __uint_as_float(pa), p1 = __uint_as_float(pb);
+  float g0 = __uint_as_float(ga), g1 = __uint_as_float(gb);
+  if (HAS_BIAS) {
+    p0 += bias_p.x;
+    p1 += bias_p.y;
+    g0 += bias_g.x;
+    g1 += bias_g.y;
   }
+  float v0 = fmaf(p0, tanh_approx(g0), p0);
+  float v1 = fmaf(p1, tanh_approx(g1), p1);
+  if (HAS_MASK) {
+    v0 *= mval;
+    v1 *= mval;
+  }
+  return sm100::pack_bf16x2(v0, v1);
 }
 
-__device__ __forceinline__ void gate_to_stage16_dispatch(int has_bias, bool has_mask, const uint32_t (&pv)[16],
-                                                         const uint32_t (&gv)[16], const float* bias_p,
-                                                         const float* bias_g, float mval, uint8_t* stage_rows) {
-  if (has_bias) {
-    if (has_mask) gate_to_stage16<true, true>(pv, gv, bias_p, bias_g, mval, stage_rows);
-    else gate_to_stage16<true, false>(pv, gv, bias_p, bias_g, mval, stage_rows);
-  } else {
-    if (has_mask) gate_to_stage16<false, true>(pv, gv, bias_p, bias_g, mval, stage_rows);
-    else gate_to_stage16<false, false>(pv, gv, bias_p, bias_g, mval, stage_rows);
+// Sixteen channels x thirty-two tokens of a gated chunk, one warp.  pl / ph (gl / gh): projection
+// (gate) accumulators of TMEM lanes 0-15 / 16-31 of the warp's quarter in the 16x256b fragment
+// layout.  Each group of eight channels leaves as one stmatrix.x4.trans: tile j = tokens 8j..8j+7,
+// memory row = channel.  `row_addr` is the shared-memory address this thread contributes for the
+// first group (its row of its tile), `row_step` the distance to the same row of the second group;
+// `m[j]` the mask of this thread's token in tile j.
+template <bool HAS_BIAS, bool HAS_MASK>
+__device__ __forceinline__ void gated16_to_stage(const uint32_t (&pl)[8], const uint32_t (&ph)[8],
+                                                 const uint32_t (&gl)[8], const uint32_t (&gh)[8],
+                                                 const float* bias_p, const float* bias_g, const float (&m)[4],
+                                                 uint32_t row_addr0, uint32_t row_addr1, int tq) {
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    float2 bp = make_float2(0.f, 0.f), bg = make_float2(0.f, 0.f);
+    if (HAS_BIAS) {
+      bp = __ldg(reinterpret_cast<const float2*>(bias_p + k * 8 + 2 * tq));
+      bg = __ldg(reinterpret_cast<const float2*>(bias_g + k * 8 + 2 * tq));
+    }
+    const uint32_t r0 = gate_pair<HAS_BIAS, HAS_MASK>(pl[4 * k], pl[4 * k + 1], gl[4 * k], gl[4 * k + 1], bp, bg, m[0]);
+    const uint32_t r1 =
+        gate_pair<HAS_BIAS, HAS_MASK>(pl[4 * k + 2], pl[4 * k + 3], gl[4 * k + 2], gl[4 * k + 3], bp, bg, m[1]);
+    const uint32_t r2 = gate_pair<HAS_BIAS, HAS_MASK>(ph[4 * k], ph[4 * k + 1], gh[4 * k], gh[4 * k + 1], bp, bg, m[2]);
+    const uint32_t r3 =
+        gate_pair<HAS_BIAS, HAS_MASK>(ph[4 * k + 2], ph[4 * k + 3], gh[4 * k + 2], gh[4 * k + 3], bp, bg, m[3]);
+    sm100::stmatrix_x4_trans(k == 0 ? row_addr0 : row_addr1, r0, r1, r2, r3);
   }
 }
 
@@ -220,9 +225,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   const int tiles_per_line = (p.n_walk + BM - 1) / BM;
   const long total_tiles = static_cast<long>(p.batch) * p.n_lines * tiles_per_line;
-  const int rot = (p.debug_skip & 32) ? 0 : static_cast<int>(blockIdx.x & 3);  // see chunk_at; bit 5: same order everywhere
+  const int rot = p.rotate_chunks ? static_cast<int>(blockIdx.x & 3) : 0;  // see chunk_at
 
   if (threadIdx.x == 0) {
+    timeline_min(p.timeline, kTlFrontStart);
     for (int s = 0; s < C::kWStages; ++s) {
       sm100::mbar_init(&ctl->w_full[s], 1);
       sm100::mbar_init(&ctl->w_empty[s], 1);
@@ -258,7 +264,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       // ---------------------------------------------------------- weight producer (TMA from L2)
       sm100::tma_prefetch_desc(&tmW);
       PipeState ps{0, 0};
-      uint32_t n_loads = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
@@ -269,22 +274,13 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               ok = false;
               break;
             }
-            // profiling probes: bit 3 reuses stale stages after the first pass (no weight traffic),
-            // bit 4 reloads only every other stage (half the weight traffic); results are wrong
-            const bool skip_load = ((p.debug_skip & 8) && n_loads >= C::kWStages) ||
-                                   ((p.debug_skip & 16) && n_loads >= C::kWStages && (n_loads & 1));
-            ++n_loads;
-            if (skip_load) {
-              sm100::mbar_arrive(&ctl->w_full[ps.stage]);
-            } else {
-              // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunk the last D rows
-              const int rows = c < C::kGated ? C::kChunkN : D;
-              ctl->armed[ps.stage] = ps.phase;
-              sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], rows * 128);
-              for (int r0 = 0; r0 < rows; r0 += C::kWBoxRows) {
-                sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes + r0 * 128, &tmW, &ctl->w_full[ps.stage], kb * 64,
-                                   c * C::kChunkN + r0);
-              }
+            // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunk the last D rows
+            const int rows = c < C::kGated ? C::kChunkN : D;
+            ctl->armed[ps.stage] = ps.phase;
+            sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], rows * 128);
+            for (int r0 = 0; r0 < rows; r0 += C::kWBoxRows) {
+              sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes + r0 * 128, &tmW, &ctl->w_full[ps.stage], kb * 64,
+                                 c * C::kChunkN + r0);
             }
             ps.advance(C::kWStages);
           }
@@ -294,8 +290,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       // ---------------------------------------------------------- UMMA issuer
       constexpr uint32_t idesc_gated = sm100::umma_idesc_bf16_f32(BM, C::kChunkN);
       constexpr uint32_t idesc_gate = sm100::umma_idesc_bf16_f32(BM, D);
-      Tracer tr;
-      tr.init(0);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
@@ -305,7 +299,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           break;
         }
         sm100::tcgen05_fence_after_sync();
-        tr.ev(1);
         const uint32_t a_addr = sm100::smem_u32(a_tiles + buf * C::kABytes);
         for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
           const int c = chunk_at<C::kGated>(ci, rot);
@@ -315,7 +308,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             break;
           }
           sm100::tcgen05_fence_after_sync();
-          tr.ev(2);
           const uint32_t d_tmem = tmem_base + acc * C::kChunkN;
           const uint32_t idesc = c < C::kGated ? idesc_gated : idesc_gate;
           for (int kb = 0; kb < C::KB; ++kb) {
@@ -336,7 +328,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           if (!ok) break;
           sm100::umma_commit(&ctl->tmem_full[acc]);
-          tr.ev(3);
           if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1;
@@ -360,7 +351,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int d_loc_mask = (1 << p.d_loc_log2) - 1;
       const int d_loc_n = 1 << p.d_loc_log2;
       uint32_t use = 0;
-      bool ok = true;
+      bool ok = true, stamped = false;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
         const int dst_x = p.dst_x0 + tc.w0;
@@ -378,15 +369,20 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const uint8_t* src = st_tiles + b * C::kStageBuf;
             if (c < C::kGated) {
               const int h = c / C::kPerHalf;   // 0: a, 1: b
-              if (!(p.debug_skip & 1)) {
-#pragma unroll 1
-                for (int k = 0; k < C::CH / 16; ++k) {
-                  const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
-                  sm100::tma_store_4d(&om.ab[d >> p.d_loc_log2], src + k * 16 * kRowPitch, dst_x, dst_y, tc.b,
-                                      h * d_loc_n + (d & d_loc_mask));
-                }
+              if (!stamped) {
+                timeline_min(p.timeline, kTlFrontFirstStore);
+                stamped = true;
               }
-            } else if (!(p.debug_skip & 2)) {
+#pragma unroll 1
+              for (int k = 0; k < C::CH / 16; ++k) {
+                const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
+                const CUtensorMap* map = &om.ab[d >> p.d_loc_log2];
+                const int plane = h * d_loc_n + (d & d_loc_mask);
+                // sixteen channel rows of each token half: (64 tokens, 16 channels) boxes, 128-byte rows
+                sm100::tma_store_4d(map, src + k * 16 * 128, dst_x, dst_y, tc.b, plane);
+                sm100::tma_store_4d(map, src + C::kHalfBytes + k * 16 * 128, dst_x + kHalfTokens, dst_y, tc.b, plane);
+              }
+            } else {
               const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
               const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
 #pragma unroll 1
@@ -402,6 +398,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
       sm100::tma_store_wait_all<0>();  // every bulk store has been performed before the CTA retires
+      timeline_max(p.timeline, kTlFrontLastStore);
     }
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
@@ -420,8 +417,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
     }
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
-    Tracer tr;
-    tr.init(1);
     uint32_t buf = 0, buf_phase = 0;
     for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
@@ -432,13 +427,12 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       for (int ps = 0; ps < PASSES; ++ps) {
         const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
         const int w = tc.w0 + r;
-        if (w < p.n_walk && !(p.debug_skip & 4)) {
+        if (w < p.n_walk) {
           raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
         } else {
           raw[ps] = make_uint4(0, 0, 0, 0);
         }
       }
-      if (lw == 0 && lane == 0) tr.ev(6);
       // normalise in registers while the tensor core still reads the previous tile
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
@@ -465,14 +459,12 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
         raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
       }
-      if (lw == 0 && lane == 0) tr.ev(7);
       bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
         break;
       }
-      if (lw == 0 && lane == 0) tr.ev(8);
       uint8_t* a_tile = a_tiles + buf * C::kABytes;
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
@@ -484,7 +476,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
-      if (lw == 0 && lane == 0) tr.ev(9);
       if (++buf == C::kABufs) {
         buf = 0;
         buf_phase ^= 1;
@@ -496,28 +487,37 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int ew = warp - kEpiWarp0;
     const int quarter = warp & 3;   // TMEM lane quarter this warp may read
     const int part = ew >> 2;       // which quarter of the chunk's columns
-    const int r = quarter * 32 + lane;  // token row of this thread inside the tile
-    Tracer tr;
-    tr.init(2);
+    const int r = quarter * 32 + lane;  // token row of this thread inside the tile (32x32b reads: the gate chunk)
+    // 16x256b fragment reads of the gated chunks: this thread holds channel pair `tq` of tokens
+    // quarter*32 + 8j + tr (j = 0..3); for stmatrix it addresses row `mr` of token tile `mj`
+    const int tq = lane & 3, tr = lane >> 2;
+    const int mj = lane >> 3, mr = lane & 7;
     uint32_t acc = 0, acc_phase = 0, use = 0;
     bool ok = true;
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
-      const int w = tc.w0 + r;
-      const bool valid = w < p.n_walk;
-      const long srow = tc.b * p.batch_rows + tc.line * p.line_rows + static_cast<long>(w) * p.walk_rows;
-      float mval = 1.0f;
-      if (valid && p.mask_kind != 0) {
-        if (p.mask_kind == 1) {
-          mval = __bfloat162float(static_cast<const __nv_bfloat16*>(p.mask)[srow]);
-        } else if (p.mask_kind == 2) {
-          mval = static_cast<const float*>(p.mask)[srow];
-        } else {
-          mval = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
+      float mval[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+      if (p.mask_kind != 0) {
+        const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int w = tc.w0 + quarter * 32 + 8 * j + tr;
+          if (w < p.n_walk) {
+            const long srow = row0 + static_cast<long>(w) * p.walk_rows;
+            if (p.mask_kind == 1) {
+              mval[j] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.mask)[srow]);
+            } else if (p.mask_kind == 2) {
+              mval[j] = static_cast<const float*>(p.mask)[srow];
+            } else {
+              mval[j] = static_cast<const uint8_t*>(p.mask)[srow] ? 1.0f : 0.0f;
+            }
+          }
         }
       }
       // a warp whose 32 tokens all carry mask 1 (the common case) skips the multiply: x * 1 is exact
-      const bool warp_has_mask = p.mask_kind != 0 && !__all_sync(0xffffffffu, mval == 1.0f);
+      const bool warp_has_mask =
+          p.mask_kind != 0 &&
+          !__all_sync(0xffffffffu, mval[0] == 1.0f && mval[1] == 1.0f && mval[2] == 1.0f && mval[3] == 1.0f);
       for (int ci = 0; ci < C::kNumChunks; ++ci) {
         const int c = chunk_at<C::kGated>(ci, rot);
         ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
@@ -534,7 +534,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           break;
         }
         sm100::tcgen05_fence_after_sync();
-        if (ew == 0 && lane == 0) tr.ev(4);
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kChunkN;
         if (c < C::kGated) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
@@ -542,18 +541,32 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           constexpr int NS = CW / 16;     // in 16-channel sub-groups
           const int colw = part * CW;
           const float* bias_p0 = p.bias + c * C::kChunkN + colw;
-          const bool has_mask = warp_has_mask;
-          uint8_t* rows = st_tiles + (use % NB) * C::kStageBuf + colw * kRowPitch + r * 2;
+          const uint32_t trow_hi = trow + (16u << 16);   // TMEM lanes 16-31 of the quarter
+          // staged layout: token half (quarter / 2), channel row, 16-byte slot of eight tokens
+          // (quarter % 2) * 4 + tile, XOR-swizzled with the row as the store descriptor expects
+          const uint32_t half_addr =
+              sm100::smem_u32(st_tiles + (use % NB) * C::kStageBuf + (quarter >> 1) * C::kHalfBytes);
+          const int slot = (quarter & 1) * 4 + mj;
 #pragma unroll
           for (int sg = 0; sg < NS; ++sg) {
-            uint32_t pv[16], gv[16];
-            sm100::tmem_ld_32x32b_x16(trow + colw + sg * 16, pv);
-            sm100::tmem_ld_32x32b_x16(trow + C::CH + colw + sg * 16, gv);
+            const int c0 = colw + sg * 16;
+            uint32_t pl[8], ph[8], gl[8], gh[8];
+            sm100::tmem_ld_16x256b_x2(trow + c0, pl);
+            sm100::tmem_ld_16x256b_x2(trow_hi + c0, ph);
+            sm100::tmem_ld_16x256b_x2(trow + C::CH + c0, gl);
+            sm100::tmem_ld_16x256b_x2(trow_hi + C::CH + c0, gh);
             sm100::tmem_ld_wait();
-            if (ew == 0 && lane == 0) tr.ev(11);
-            gate_to_stage16_dispatch(p.has_bias, has_mask, pv, gv, bias_p0 + sg * 16, bias_p0 + C::CH + sg * 16, mval,
-                                     rows + sg * 16 * kRowPitch);
-            if (ew == 0 && lane == 0) tr.ev(12);
+            const int row_a = c0 + mr, row_b = c0 + 8 + mr;
+            const uint32_t addr_a = half_addr + row_a * 128 + ((slot ^ (row_a & 7)) << 4);
+            const uint32_t addr_b = half_addr + row_b * 128 + ((slot ^ (row_b & 7)) << 4);
+            const float* bp = bias_p0 + sg * 16;
+            if (p.has_bias) {
+              if (warp_has_mask) gated16_to_stage<true, true>(pl, ph, gl, gh, bp, bp + C::CH, mval, addr_a, addr_b, tq);
+              else gated16_to_stage<true, false>(pl, ph, gl, gh, bp, bp + C::CH, mval, addr_a, addr_b, tq);
+            } else {
+              if (warp_has_mask) gated16_to_stage<false, true>(pl, ph, gl, gh, bp, bp + C::CH, mval, addr_a, addr_b, tq);
+              else gated16_to_stage<false, false>(pl, ph, gl, gh, bp, bp + C::CH, mval, addr_a, addr_b, tq);
+            }
           }
         } else {
           // output-gate chunk: sigmoid only, token-major, into (128 token x 64 channel) boxes
@@ -583,7 +596,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           for (int u = 0; u < n_use; ++u) sm100::mbar_arrive(&ctl->st_full[(use + u) % NB]);
         }
         use += n_use;
-        if (ew == 0 && lane == 0) tr.ev(5);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -615,16 +627,6 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
-// Profiling aid: point the projection kernel's CTA-0 timeline at a device buffer of `cap` uint64
-// records (nullptr switches it off).  Not part of the C ABI.
-extern "C" int trimul_debug_set_gated_proj_trace(void* buf, unsigned int cap) {
-  unsigned long long* b = static_cast<unsigned long long*>(buf);
-  cap /= 3;  // three tracing roles share the buffer
-  if (cudaMemcpyToSymbol(g_trace_buf, &b, sizeof(b)) != cudaSuccess) return -1;
-  if (cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof(cap)) != cudaSuccess) return -1;
-  return 0;
-}
-
 int gated_proj_smem_bytes(int D) {
   if (D == 128) return smem_bytes<128>();
   if (D == 256) return smem_bytes<256>();

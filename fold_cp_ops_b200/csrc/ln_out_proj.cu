@@ -95,6 +95,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const long my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
+    timeline_min(p.timeline, kTlOutStart);
     for (int s = 0; s < C::kStages; ++s) {
       sm100::mbar_init(&ctl->full[s], 1);
       sm100::mbar_init(&ctl->empty[s], 1 + 8);  // tcgen05.commit + one arrive per statistics warp
@@ -212,13 +213,9 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             ok = false;
             break;
           }
-          if (p.debug_skip & 2) {
-            sm100::mbar_arrive(&ctl->g_full[slot]);   // profiling probe: no gate traffic
-          } else {
-            ctl->g_armed[slot] = ph;
-            sm100::mbar_arrive_expect_tx(&ctl->g_full[slot], kBoxBytes);
-            sm100::tma_load_2d(boxes + slot * kBoxBytes, &tmG, &ctl->g_full[slot], jb * 64, static_cast<int>(m0));
-          }
+          ctl->g_armed[slot] = ph;
+          sm100::mbar_arrive_expect_tx(&ctl->g_full[slot], kBoxBytes);
+          sm100::tma_load_2d(boxes + slot * kBoxBytes, &tmG, &ctl->g_full[slot], jb * 64, static_cast<int>(m0));
         }
         seq += C::NBT;
       }
@@ -241,9 +238,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             ok = false;
             break;
           }
-          if (!(p.debug_skip & 4)) {
-            sm100::tma_store_2d(&tmO, boxes + slot * kBoxBytes, jb * 64, static_cast<int>(m0));
-          }
+          sm100::tma_store_2d(&tmO, boxes + slot * kBoxBytes, jb * 64, static_cast<int>(m0));
           sm100::tma_store_commit();
           sm100::tma_store_wait_read<0>();
           sm100::mbar_arrive(&ctl->g_free[slot]);
@@ -251,6 +246,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         seq += C::NBT;
       }
       sm100::tma_store_wait_all<0>();
+      timeline_max(p.timeline, kTlOutEnd);
     }
   } else if (warp >= kStatWarp0) {
     // ------------------------------------------------------------ statistics (8 warps)
@@ -378,68 +374,54 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       sm100::tcgen05_fence_after_sync();
       const float2 rs = ctl->stat[acc][r];  // (rstd, -mean * rstd) of this thread's token
       const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * D;
-      if (!(p.debug_skip & 8)) {
-        // TMEM reads are software-pipelined one 16-channel group ahead, across the boxes of the half
-        uint32_t pa[16], pb[16];
-        sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64, pa);
+      // TMEM reads are software-pipelined one 16-channel group ahead, across the boxes of the half
+      uint32_t pa[16], pb[16];
+      sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64, pa);
 #pragma unroll
-        for (int i = 0; i < NBS; ++i) {
-          const int jb = set * NBS + i;
-          const uint32_t sq = seq0 + jb;
-          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
-          ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            report_timeout(p.status, kKernelOutProj, 8, jb);
-            break;
-          }
-          uint8_t* row = boxes + slot * kBoxBytes + r * 128;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int gi = i * 4 + g;
-            sm100::tmem_ld_wait();
-            if (gi + 1 < NBS * 4) {
-              if ((gi & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pb);
-              else sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pa);
-            }
-            const float2* cdp = &ctl->cd[jb * 64 + g * 16];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              uint4* slot_ptr = reinterpret_cast<uint4*>(row + (((2 * g + hh) ^ sw) << 4));
-              const uint4 gt = *slot_ptr;
-              const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
-              uint32_t ow[4];
-#pragma unroll
-              for (int e2 = 0; e2 < 4; ++e2) {
-                const int e = hh * 8 + e2 * 2;
-                const float4 cd2 = *reinterpret_cast<const float4*>(cdp + e);  // (c, d) of two channels, same for all lanes
-                const float a0 = __uint_as_float((gi & 1) == 0 ? pa[e] : pb[e]);
-                const float a1 = __uint_as_float((gi & 1) == 0 ? pa[e + 1] : pb[e + 1]);
-                const float y0 = fmaf(a0, rs.x, fmaf(rs.y, cd2.x, cd2.y));
-                const float y1 = fmaf(a1, rs.x, fmaf(rs.y, cd2.z, cd2.w));
-                ow[e2] = sm100::pack_bf16x2(y0 * sm100::bf16_lo(gw[e2]), y1 * sm100::bf16_hi(gw[e2]));
-              }
-              *slot_ptr = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-            }
-          }
-          sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk store
-          __syncwarp();
-          if (lane == 0) sm100::mbar_arrive(&ctl->o_full[slot]);
+      for (int i = 0; i < NBS; ++i) {
+        const int jb = set * NBS + i;
+        const uint32_t sq = seq0 + jb;
+        const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
+        ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          report_timeout(p.status, kKernelOutProj, 8, jb);
+          break;
         }
-        if (!ok) break;
-      } else {
-        // profiling probe: no epilogue work, the boxes pass through untouched
-        for (int i = 0; i < NBS; ++i) {
-          const uint32_t sq = seq0 + set * NBS + i;
-          const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
-          ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          __syncwarp();
-          if (lane == 0) sm100::mbar_arrive(&ctl->o_full[slot]);
+        uint8_t* row = boxes + slot * kBoxBytes + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int gi = i * 4 + g;
+          sm100::tmem_ld_wait();
+          if (gi + 1 < NBS * 4) {
+            if ((gi & 1) == 0) sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pb);
+            else sm100::tmem_ld_32x32b_x16(trow + set * NBS * 64 + (gi + 1) * 16, pa);
+          }
+          const float2* cdp = &ctl->cd[jb * 64 + g * 16];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint4* slot_ptr = reinterpret_cast<uint4*>(row + (((2 * g + hh) ^ sw) << 4));
+            const uint4 gt = *slot_ptr;
+            const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const int e = hh * 8 + e2 * 2;
+              const float4 cd2 = *reinterpret_cast<const float4*>(cdp + e);  // (c, d) of two channels, same for all lanes
+              const float a0 = __uint_as_float((gi & 1) == 0 ? pa[e] : pb[e]);
+              const float a1 = __uint_as_float((gi & 1) == 0 ? pa[e + 1] : pb[e + 1]);
+              const float y0 = fmaf(a0, rs.x, fmaf(rs.y, cd2.x, cd2.y));
+              const float y1 = fmaf(a1, rs.x, fmaf(rs.y, cd2.z, cd2.w));
+              ow[e2] = sm100::pack_bf16x2(y0 * sm100::bf16_lo(gw[e2]), y1 * sm100::bf16_hi(gw[e2]));
+            }
+            *slot_ptr = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
         }
-        if (!ok) break;
+        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk store
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl->o_full[slot]);
       }
+      if (!ok) break;
       seq0 += C::NBT;
       sm100::tcgen05_fence_before_sync();
       __syncwarp();

@@ -27,10 +27,11 @@ __global__ void peer_signal_kernel(PeerPtrs flags, int cp, int slot) {
 }
 
 __global__ void peer_wait_kernel(const unsigned long long* local_flags, int slot, unsigned long long expected,
-                                 DeviceStatus* status, uint64_t timeout_ns) {
+                                 DeviceStatus* status, unsigned long long* timeline, uint64_t timeout_ns) {
   if (threadIdx.x != 0) return;
   const unsigned long long* f = local_flags + slot;
   const uint64_t t0 = sm100::globaltimer_ns();
+  if (timeline != nullptr && slot < 3) timeline[kTlWaitBase + 2 * slot] = t0;
   unsigned long long v;
   uint32_t spins = 0;
   while (true) {
@@ -42,6 +43,7 @@ __global__ void peer_wait_kernel(const unsigned long long* local_flags, int slot
     }
     __nanosleep(64);
   }
+  if (timeline != nullptr && slot < 3) timeline[kTlWaitBase + 2 * slot + 1] = sm100::globaltimer_ns();
 }
 
 }  // namespace trimul
@@ -59,11 +61,12 @@ int trimul_sm100_peer_signal(void* const* flag_peers, int32_t cp, int32_t slot, 
 }
 
 int trimul_sm100_peer_wait(const void* local_flags, int32_t slot, uint64_t expected, trimul_status_t* status,
-                           uint64_t timeout_ns, trimul_stream_t stream) {
+                           uint64_t* timeline, uint64_t timeout_ns, trimul_stream_t stream) {
   if (local_flags == nullptr || slot < 0 || slot >= 16) return TRIMUL_ERR_INVALID_ARGUMENT;
   trimul::peer_wait_kernel<<<1, 32, 0, stream>>>(static_cast<const unsigned long long*>(local_flags), slot,
                                                  static_cast<unsigned long long>(expected),
                                                  reinterpret_cast<trimul::DeviceStatus*>(status),
+                                                 reinterpret_cast<unsigned long long*>(timeline),
                                                  timeout_ns ? timeout_ns : 2000000000ull);
   return cudaGetLastError() == cudaSuccess ? TRIMUL_OK : TRIMUL_ERR_CUDA;
 }

@@ -283,8 +283,33 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+// 16x256b: the warp reads SIXTEEN TMEM lanes starting at the lane in `taddr` (offset 0 or 16 inside
+// the warp's quarter) in the accumulator-fragment layout of mma: with t = lane id of the thread,
+//   r[4k + 0], r[4k + 1] = TMEM lane t/4,     columns 8k + 2(t%4), 8k + 2(t%4) + 1
+//   r[4k + 2], r[4k + 3] = TMEM lane t/4 + 8, the same two columns
+// for k = 0, 1 (.x2 = 16 columns).  A pair of neighbouring columns packed to bf16x2 is exactly the
+// register a thread contributes to an 8 x 8 stmatrix tile.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Four 8 x 8 tiles of 16-bit elements, stored TRANSPOSED: thread t holds, for tile j, the pair
+// (row t/4, columns 2(t%4), 2(t%4)+1) in r_j (low half = the even column); threads 8j .. 8j+7 give the
+// shared-memory addresses of the tile's eight 16-byte rows, and memory row c receives column c of
+// the tile (eight consecutive ROW indices).  With rows = tokens and columns = channels this writes
+// channel-major data straight from a token-per-lane accumulator fragment.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t smem_row_addr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                                  uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.x4.trans.m8n8.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(smem_row_addr), "r"(r0),
+               "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
 }
 
 // ------------------------------------------------------------------------------------------

@@ -63,6 +63,7 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_k = (p.n_k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
+    timeline_min(p.timeline, kTlContractStart);
     for (int s = 0; s < kStages; ++s) {
       sm100::mbar_init(&ctl->full[s], 1);
       sm100::mbar_init(&ctl->empty[s], 1);
@@ -184,7 +185,10 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     // every store this thread issued must have been performed before the CTA exits
-    if (lane == 0) sm100::tma_store_wait_all<0>();
+    if (lane == 0) {
+      sm100::tma_store_wait_all<0>();
+      timeline_max(p.timeline, kTlContractLastStore);
+    }
   }
 
   // ------------------------------------------------------------------ teardown

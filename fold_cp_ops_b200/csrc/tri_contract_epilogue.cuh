@@ -28,7 +28,7 @@ __device__ __forceinline__ void store_band(const TriContractArgs& p, const TriOu
   const int i_l = i - i_blk * p.ni_loc;
   // the band can go out as TMA stores when it lies inside the matrix and inside one owner's row block
   const int iw_blk = i0w / p.ni_loc;
-  const bool band_ok = !p.direct_stores && (i0w + 31 < p.n_i) && ((i0w + 31) / p.ni_loc == iw_blk);
+  const bool band_ok = (i0w + 31 < p.n_i) && ((i0w + 31) / p.ni_loc == iw_blk);
   // destination plane index on the owner: (chan_offset + d_loc) * B + b  == chan_offset*B + plane
   const long dst_plane = static_cast<long>(p.chan_offset) * p.batch + plane;
 #pragma unroll 1

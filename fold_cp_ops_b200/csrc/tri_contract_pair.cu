@@ -65,6 +65,7 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int num_k = (p.n_k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
+    timeline_min(p.timeline, kTlContractStart);
     for (int s = 0; s < kStages; ++s) {
       sm100::mbar_init(&ctl->full[s], 1);    // first CTA: its producer's arrive + the bytes of both CTAs' loads
       sm100::mbar_init(&ctl->empty[s], 1);   // tcgen05.commit, delivered to both CTAs
@@ -185,7 +186,10 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         acc_phase ^= 1;
       }
     }
-    if (lane == 0) sm100::tma_store_wait_all<0>();
+    if (lane == 0) {
+      sm100::tma_store_wait_all<0>();
+      timeline_max(p.timeline, kTlContractLastStore);
+    }
   }
 
   // ------------------------------------------------------------------ teardown

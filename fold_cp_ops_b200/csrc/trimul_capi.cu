@@ -7,6 +7,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <new>
+
 #include "../../include/trimul_sm100.h"
 #include "trimul_kernels.h"
 
@@ -75,13 +77,6 @@ int num_sms_current() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
   }
   return cached[dev];
-}
-
-// Profiling aid: TRIMUL_DEBUG_SKIP=<bits> makes a kernel leave out one of its memory streams so its
-// cost can be measured in isolation (results are then wrong by construction).  Unset in normal use.
-int debug_skip_bits() {
-  const char* e = getenv("TRIMUL_DEBUG_SKIP");
-  return e ? atoi(e) : 0;
 }
 
 struct Derived {
@@ -232,7 +227,253 @@ __global__ void pack_out_weights_kernel(int d, const __nv_bfloat16* w_out, const
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// the three launches, split into "encode once" (build_*) and "launch" (launch_*)
+// ---------------------------------------------------------------------------------------------
+struct FrontPart {
+  CUtensorMap tmW;
+  trimul::GatedOutMaps maps;
+  trimul::GatedProjArgs args;
+};
+
+struct ContractPart {
+  CUtensorMap tmA, tmB;
+  trimul::TriOutMaps maps;
+  trimul::TriContractArgs args;
+  bool pair;
+};
+
+struct OutPart {
+  CUtensorMap tmW, tmT, tmG, tmO;
+  const void* tmO_for;  // the `out` pointer tmO was encoded for (re-encoded only when it changes)
+  trimul::OutProjArgs args;
+};
+
+constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
+
+int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning_t* tuning, const float* ln_w,
+                const float* ln_b, const void* w_packed, const float* bias_packed, void* const* ab_peers, void* gate_out,
+                trimul_status_t* status, uint64_t* timeline, uint64_t timeout_ns, FrontPart* out) {
+  if (!ln_w || !w_packed || !ab_peers || !gate_out) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: NULL pointer");
+  const int D = geom->d;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(5 * D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    int rc = make_tmap(&out->tmW, w_packed, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  trimul::GatedProjArgs& a = out->args;
+  memset(&a, 0, sizeof(a));
+  a.ln_w = ln_w;
+  a.ln_b = ln_b;
+  a.bias = bias_packed;
+  a.has_bias = bias_packed != nullptr ? 1 : 0;
+  a.eps = geom->eps;
+  a.D = D;
+  a.batch = geom->batch;
+  if (geom->direction == TRIMUL_OUTGOING && geom->cp1 == 1 && static_cast<long>(d.ni_loc) * d.nj_loc > 0x7fffffffL)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token block too large");
+  trimul_reshard_plan_t plan;
+  derive_plan(geom, d, &plan);
+  a.batch_rows = plan.batch_rows;
+  a.n_lines = plan.n_lines;
+  a.n_walk = plan.n_walk;
+  a.line_rows = plan.line_rows;
+  a.walk_rows = plan.walk_rows;
+  a.dst_base = plan.dst_base;
+  a.dst_line = plan.dst_line;
+  for (int s = 0; s < d.cp; ++s) {
+    if (ab_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ab_peers[%d] is NULL", s);
+    a.ab.ptr[s] = ab_peers[s];
+  }
+  a.d_loc_log2 = d.d_loc_log2;
+  a.plane_elems = plan.plane_elems;
+  a.gate_out = gate_out;
+  if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d: a plane must hold fewer than 2^31 tokens", geom->n);
+  memset(&out->maps, 0, sizeof(out->maps));
+  {
+    // Store maps.  a|b: every owner's operand buffer as (x, y, batch, 2*D_loc planes); x is clipped
+    // at the end of this rank's walk so a ragged tile cannot reach a neighbour's tokens.  Boxes are
+    // 64 tokens x 16 channel planes with the 128-byte swizzle (the layout stmatrix fills).
+    const uint64_t n = static_cast<uint64_t>(geom->n);
+    const bool flat = plan.dst_line == 0;  // whole block contiguous: one line, x runs over the plane
+    a.dst_x0 = static_cast<int>(flat ? plan.dst_base : plan.dst_base % plan.dst_line);
+    a.dst_y0 = static_cast<int>(flat ? 0 : plan.dst_base / plan.dst_line);
+    const uint64_t dims[4] = {static_cast<uint64_t>(a.dst_x0) + static_cast<uint64_t>(plan.n_walk), flat ? 1 : n,
+                              static_cast<uint64_t>(geom->batch), static_cast<uint64_t>(2 * d.d_loc)};
+    const uint64_t strides[3] = {flat ? n * n * 2 : n * 2, n * n * 2, n * n * 2 * geom->batch};
+    const uint32_t box[4] = {64, 1, 1, 16};
+    for (int s = 0; s < d.cp; ++s) {
+      int rc = make_tmap(&out->maps.ab[s], ab_peers[s], 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != TRIMUL_OK) return rc;
+    }
+    // gate: local (rows, D) buffer as (D, walk | line, line | walk, batch), the smaller row stride first
+    const uint64_t row_b = static_cast<uint64_t>(D) * 2;
+    const uint64_t line_stride =
+        (plan.n_lines > 1 ? static_cast<uint64_t>(plan.line_rows) : static_cast<uint64_t>(plan.batch_rows)) * row_b;
+    const uint64_t walk_stride = static_cast<uint64_t>(plan.walk_rows) * row_b;
+    const uint64_t batch_stride = static_cast<uint64_t>(plan.batch_rows) * row_b;
+    const bool walk_first = walk_stride <= line_stride;
+    a.gate_walk_dim = walk_first ? 1 : 2;
+    const uint64_t gdims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(walk_first ? plan.n_walk : plan.n_lines),
+                               static_cast<uint64_t>(walk_first ? plan.n_lines : plan.n_walk),
+                               static_cast<uint64_t>(geom->batch)};
+    const uint64_t gstr[3] = {walk_first ? walk_stride : line_stride, walk_first ? line_stride : walk_stride, batch_stride};
+    const uint32_t gbox[4] = {64, walk_first ? 128u : 1u, walk_first ? 1u : 128u, 1};
+    int rc = make_tmap(&out->maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  a.rotate_chunks = (tuning != nullptr && tuning->front_fixed_order) ? 0 : 1;
+  a.timeline = reinterpret_cast<unsigned long long*>(timeline);
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : kDefaultTimeoutNs;
+  return TRIMUL_OK;
+}
+
+int launch_front(FrontPart& part, const void* x, const void* mask, int32_t mask_kind, int num_sms, cudaStream_t stream) {
+  if (x == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: x is NULL");
+  if (mask_kind < 0 || mask_kind > 3 || (mask_kind != 0 && mask == nullptr))
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: bad mask_kind %d", mask_kind);
+  part.args.x = x;
+  part.args.mask = mask_kind ? mask : nullptr;
+  part.args.mask_kind = mask_kind;
+  cudaError_t e = trimul::launch_gated_proj(part.tmW, part.maps, part.args, num_sms, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "ln_gated_proj launch");
+  return TRIMUL_OK;
+}
+
+int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tuning_t* tuning, const void* ab_local,
+                   void* const* tri_peers, trimul_status_t* status, uint64_t* timeline, uint64_t timeout_ns, int num_sms,
+                   ContractPart* out) {
+  if (!ab_local || !tri_peers) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_contract: NULL pointer");
+  const int form = tuning != nullptr ? tuning->contract_form : TRIMUL_CONTRACT_DEFAULT;
+  if (form < TRIMUL_CONTRACT_DEFAULT || form > TRIMUL_CONTRACT_PAIR)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_form=%d is not one of TRIMUL_CONTRACT_*", form);
+  // default: CTA pairs (256 x 256 tiles over two SMs) -- faster than 128 x 256 single-CTA tiles at
+  // every shape measured -- unless the device has a single SM
+  out->pair = form == TRIMUL_CONTRACT_PAIR || (form == TRIMUL_CONTRACT_DEFAULT && num_sms >= 2);
+  if (out->pair && num_sms < 2) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "the CTA-pair contraction needs two SMs");
+  const uint64_t n = static_cast<uint64_t>(geom->n);
+  const uint64_t planes = static_cast<uint64_t>(d.d_loc) * geom->batch;
+  {
+    // A: 128-row boxes; B: 256-row boxes for the single-CTA form, two 128-row halves for a pair
+    const uint64_t dims[3] = {n, n, planes};
+    const uint64_t strides[2] = {n * 2, n * n * 2};
+    const uint32_t boxA[3] = {64, 128, 1};
+    const uint32_t boxB[3] = {64, out->pair ? 128u : 256u, 1};
+    int rc = make_tmap(&out->tmA, ab_local, 3, dims, strides, boxA);
+    if (rc != TRIMUL_OK) return rc;
+    const uint8_t* b_base = static_cast<const uint8_t*>(ab_local) + planes * n * n * 2;
+    rc = make_tmap(&out->tmB, b_base, 3, dims, strides, boxB);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  trimul::TriContractArgs& a = out->args;
+  memset(&a, 0, sizeof(a));
+  a.planes = static_cast<int>(planes);
+  a.batch = geom->batch;
+  a.n_i = a.n_j = a.n_k = geom->n;
+  for (int s = 0; s < d.cp; ++s) {
+    if (tri_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_peers[%d] is NULL", s);
+    a.out.ptr[s] = tri_peers[s];
+  }
+  a.ni_loc = d.ni_loc;
+  a.nj_loc = d.nj_loc;
+  a.cp1 = geom->cp1;
+  a.chan_offset = geom->rank * d.d_loc;
+  memset(&out->maps, 0, sizeof(out->maps));
+  {
+    // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)
+    const uint64_t odims[3] = {static_cast<uint64_t>(d.nj_loc), static_cast<uint64_t>(d.ni_loc),
+                               static_cast<uint64_t>(geom->d) * geom->batch};
+    const uint64_t ostr[2] = {static_cast<uint64_t>(d.nj_loc) * 2, static_cast<uint64_t>(d.nj_loc) * d.ni_loc * 2};
+    const uint32_t obox[3] = {64, 32, 1};
+    for (int s = 0; s < d.cp; ++s) {
+      int rc = make_tmap(&out->maps.map[s], tri_peers[s], 3, odims, ostr, obox);
+      if (rc != TRIMUL_OK) return rc;
+    }
+  }
+  a.timeline = reinterpret_cast<unsigned long long*>(timeline);
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : kDefaultTimeoutNs;
+  return TRIMUL_OK;
+}
+
+int launch_contract(const ContractPart& part, int num_sms, cudaStream_t stream) {
+  cudaError_t e = part.pair ? trimul::launch_tri_contract_pair(part.tmA, part.tmB, part.maps, part.args, num_sms, stream)
+                            : trimul::launch_tri_contract(part.tmA, part.tmB, part.maps, part.args, num_sms, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "tri_contract launch");
+  return TRIMUL_OK;
+}
+
+int encode_out_map(CUtensorMap* map, const void* base, int D, long rows) {
+  // gate and out, token-major (rows, D): boxes of 64 channels x 128 tokens (128-byte rows)
+  const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(rows)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+  const uint32_t box[2] = {64, 128};
+  return make_tmap(map, base, 2, dims, strides, box);
+}
+
+int build_out(const trimul_geom_t* geom, const Derived& d, const void* tri_local, const void* gate, const void* w_fold,
+              const float* cd, trimul_status_t* status, uint64_t* timeline, uint64_t timeout_ns, OutPart* out) {
+  if (!tri_local || !gate || !w_fold || !cd) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_out_proj: NULL pointer");
+  const int D = geom->d;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    int rc = make_tmap(&out->tmW, w_fold, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  {
+    // tri as (tokens contiguous, channels): the tile is consumed token-major exactly as stored
+    const uint64_t dims[2] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(D)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d.rows) * 2};
+    const uint32_t box[2] = {64, 64};
+    int rc = make_tmap(&out->tmT, tri_local, 2, dims, strides, box);
+    if (rc != TRIMUL_OK) return rc;
+  }
+  int rc = encode_out_map(&out->tmG, gate, D, d.rows);
+  if (rc != TRIMUL_OK) return rc;
+  out->tmO_for = nullptr;
+  trimul::OutProjArgs& a = out->args;
+  memset(&a, 0, sizeof(a));
+  a.gate = gate;
+  a.cd = cd;
+  a.eps = geom->eps;
+  a.D = D;
+  a.rows = d.rows;
+  a.timeline = reinterpret_cast<unsigned long long*>(timeline);
+  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
+  a.timeout_ns = timeout_ns ? timeout_ns : kDefaultTimeoutNs;
+  return TRIMUL_OK;
+}
+
+int launch_out(OutPart& part, void* out, int num_sms, cudaStream_t stream) {
+  if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_out_proj: out is NULL");
+  if (part.tmO_for != out) {  // a caller that reuses its output buffer pays for this once
+    int rc = encode_out_map(&part.tmO, out, part.args.D, part.args.rows);
+    if (rc != TRIMUL_OK) return rc;
+    part.tmO_for = out;
+  }
+  part.args.out = out;
+  cudaError_t e = trimul::launch_out_proj(part.tmW, part.tmT, part.tmG, part.tmO, part.args, num_sms, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "ln_out_proj launch");
+  return TRIMUL_OK;
+}
+
 }  // namespace
+
+// The opaque plan of the C ABI: one rank's three launches for a fixed geometry and set of buffers.
+struct trimul_plan {
+  int device;
+  int num_sms;
+  FrontPart front;
+  ContractPart contract;
+  OutPart out;
+};
 
 namespace trimul {
 // Lets other translation units of the library leave a message in the slot trimul_sm100_last_error reads.
@@ -307,165 +548,30 @@ int trimul_sm100_pack_out_weights(int32_t d, const void* w_out, const float* ln_
   return TRIMUL_OK;
 }
 
-int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
-                               const float* ln_w, const float* ln_b, const void* w_packed,
+int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const trimul_tuning_t* tuning, const void* x, const void* mask,
+                               int32_t mask_kind, const float* ln_w, const float* ln_b, const void* w_packed,
                                const float* bias_packed, void* const* ab_peers, void* gate_out,
                                trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
   Derived d;
   int rc = check_geom(geom, &d);
   if (rc != TRIMUL_OK) return rc;
-  if (!x || !ln_w || !w_packed || !ab_peers || !gate_out)
-    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: NULL pointer");
-  if (mask_kind < 0 || mask_kind > 3 || (mask_kind != 0 && mask == nullptr))
-    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_gated_proj: bad mask_kind %d", mask_kind);
-  const int D = geom->d;
-  CUtensorMap tmW;
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(5 * D)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
-    rc = make_tmap(&tmW, w_packed, 2, dims, strides, box);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  trimul::GatedProjArgs a;
-  memset(&a, 0, sizeof(a));
-  a.x = x;
-  a.mask = mask_kind ? mask : nullptr;
-  a.mask_kind = mask_kind;
-  a.ln_w = ln_w;
-  a.ln_b = ln_b;
-  a.bias = bias_packed;
-  a.has_bias = bias_packed != nullptr ? 1 : 0;
-  a.eps = geom->eps;
-  a.D = D;
-  a.batch = geom->batch;
-  if (geom->direction == TRIMUL_OUTGOING && geom->cp1 == 1 && static_cast<long>(d.ni_loc) * d.nj_loc > 0x7fffffffL)
-    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token block too large");
-  trimul_reshard_plan_t plan;
-  derive_plan(geom, d, &plan);
-  a.batch_rows = plan.batch_rows;
-  a.n_lines = plan.n_lines;
-  a.n_walk = plan.n_walk;
-  a.line_rows = plan.line_rows;
-  a.walk_rows = plan.walk_rows;
-  a.dst_base = plan.dst_base;
-  a.dst_line = plan.dst_line;
-  for (int s = 0; s < d.cp; ++s) {
-    if (ab_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ab_peers[%d] is NULL", s);
-    a.ab.ptr[s] = ab_peers[s];
-  }
-  a.d_loc_log2 = d.d_loc_log2;
-  a.plane_elems = plan.plane_elems;
-  a.gate_out = gate_out;
-  if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
-    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "n=%d: a plane must hold fewer than 2^31 tokens", geom->n);
-  trimul::GatedOutMaps maps;
-  memset(&maps, 0, sizeof(maps));
-  {
-    // Store maps.  a|b: every owner's operand buffer as (x, y, batch, 2*D_loc planes); x is clipped
-    // at the end of this rank's walk so a ragged tile cannot reach a neighbour's tokens.
-    const uint64_t n = static_cast<uint64_t>(geom->n);
-    const bool flat = plan.dst_line == 0;  // whole block contiguous: one line, x runs over the plane
-    a.dst_x0 = static_cast<int>(flat ? plan.dst_base : plan.dst_base % plan.dst_line);
-    a.dst_y0 = static_cast<int>(flat ? 0 : plan.dst_base / plan.dst_line);
-    const uint64_t dims[4] = {static_cast<uint64_t>(a.dst_x0) + static_cast<uint64_t>(plan.n_walk), flat ? 1 : n,
-                              static_cast<uint64_t>(geom->batch), static_cast<uint64_t>(2 * d.d_loc)};
-    const uint64_t strides[3] = {flat ? n * n * 2 : n * 2, n * n * 2, n * n * 2 * geom->batch};
-    const uint32_t box[4] = {128, 1, 1, 16};
-    for (int s = 0; s < d.cp; ++s) {
-      rc = make_tmap(&maps.ab[s], ab_peers[s], 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
-      if (rc != TRIMUL_OK) return rc;
-    }
-    // gate: local (rows, D) buffer as (D, walk | line, line | walk, batch), the smaller row stride first
-    const uint64_t row_b = static_cast<uint64_t>(D) * 2;
-    const uint64_t line_stride = (plan.n_lines > 1 ? static_cast<uint64_t>(plan.line_rows) : static_cast<uint64_t>(plan.batch_rows)) * row_b;
-    const uint64_t walk_stride = static_cast<uint64_t>(plan.walk_rows) * row_b;
-    const uint64_t batch_stride = static_cast<uint64_t>(plan.batch_rows) * row_b;
-    const bool walk_first = walk_stride <= line_stride;
-    a.gate_walk_dim = walk_first ? 1 : 2;
-    const uint64_t gdims[4] = {static_cast<uint64_t>(D),
-                               static_cast<uint64_t>(walk_first ? plan.n_walk : plan.n_lines),
-                               static_cast<uint64_t>(walk_first ? plan.n_lines : plan.n_walk),
-                               static_cast<uint64_t>(geom->batch)};
-    const uint64_t gstr[3] = {walk_first ? walk_stride : line_stride, walk_first ? line_stride : walk_stride, batch_stride};
-    const uint32_t gbox[4] = {64, walk_first ? 128u : 1u, walk_first ? 1u : 128u, 1};
-    rc = make_tmap(&maps.gate, gate_out, 4, gdims, gstr, gbox, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  a.debug_skip = (debug_skip_bits() & 7) | ((debug_skip_bits() >> 10) & 7) << 3;  // bits 10-11: weight-stream probes, 12: fixed chunk order
-  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
-  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_gated_proj(tmW, maps, a, num_sms_current(), stream);
-  if (e != cudaSuccess) return cuda_fail(e, "ln_gated_proj launch");
-  return TRIMUL_OK;
+  FrontPart part;
+  rc = build_front(geom, d, tuning, ln_w, ln_b, w_packed, bias_packed, ab_peers, gate_out, status, nullptr, timeout_ns,
+                   &part);
+  if (rc != TRIMUL_OK) return rc;
+  return launch_front(part, x, mask, mask_kind, num_sms_current(), stream);
 }
 
-int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, void* const* tri_peers,
-                              trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream) {
+int trimul_sm100_tri_contract(const trimul_geom_t* geom, const trimul_tuning_t* tuning, const void* ab_local,
+                              void* const* tri_peers, trimul_status_t* status, uint64_t timeout_ns,
+                              trimul_stream_t stream) {
   Derived d;
   int rc = check_geom(geom, &d);
   if (rc != TRIMUL_OK) return rc;
-  if (!ab_local || !tri_peers) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_contract: NULL pointer");
-  const uint64_t n = static_cast<uint64_t>(geom->n);
-  const uint64_t planes = static_cast<uint64_t>(d.d_loc) * geom->batch;
-  CUtensorMap tmA, tmB;
-  {
-    const uint64_t dims[3] = {n, n, planes};
-    const uint64_t strides[2] = {n * 2, n * n * 2};
-    const uint32_t boxA[3] = {64, 128, 1};
-    const uint32_t boxB[3] = {64, 256, 1};
-    rc = make_tmap(&tmA, ab_local, 3, dims, strides, boxA);
-    if (rc != TRIMUL_OK) return rc;
-    const uint8_t* b_base = static_cast<const uint8_t*>(ab_local) + planes * n * n * 2;
-    rc = make_tmap(&tmB, b_base, 3, dims, strides, boxB);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  trimul::TriContractArgs a;
-  memset(&a, 0, sizeof(a));
-  a.planes = static_cast<int>(planes);
-  a.batch = geom->batch;
-  a.n_i = a.n_j = a.n_k = geom->n;
-  for (int s = 0; s < d.cp; ++s) {
-    if (tri_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tri_peers[%d] is NULL", s);
-    a.out.ptr[s] = tri_peers[s];
-  }
-  a.ni_loc = d.ni_loc;
-  a.nj_loc = d.nj_loc;
-  a.cp1 = geom->cp1;
-  a.chan_offset = geom->rank * d.d_loc;
-  a.direct_stores = (debug_skip_bits() >> 9) & 1;
-  trimul::TriOutMaps out_maps;
-  memset(&out_maps, 0, sizeof(out_maps));
-  {
-    // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)
-    const uint64_t odims[3] = {static_cast<uint64_t>(d.nj_loc), static_cast<uint64_t>(d.ni_loc),
-                               static_cast<uint64_t>(geom->d) * geom->batch};
-    const uint64_t ostr[2] = {static_cast<uint64_t>(d.nj_loc) * 2, static_cast<uint64_t>(d.nj_loc) * d.ni_loc * 2};
-    const uint32_t obox[3] = {64, 32, 1};
-    for (int s = 0; s < d.cp; ++s) {
-      rc = make_tmap(&out_maps.map[s], tri_peers[s], 3, odims, ostr, obox);
-      if (rc != TRIMUL_OK) return rc;
-    }
-  }
-  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
-  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e;
-  if (!((debug_skip_bits() >> 14) & 1) && num_sms_current() >= 2) {
-    // CTA-pair form (256 x 256 tile per pair of SMs; bit 14 of the profiling mask selects the
-    // single-CTA 128 x 256 kernel instead): B is loaded in two halves of 128 rows
-    CUtensorMap tmBh;
-    const uint64_t dims[3] = {n, n, planes};
-    const uint64_t strides[2] = {n * 2, n * n * 2};
-    const uint32_t boxH[3] = {64, 128, 1};
-    const uint8_t* b_base = static_cast<const uint8_t*>(ab_local) + planes * n * n * 2;
-    rc = make_tmap(&tmBh, b_base, 3, dims, strides, boxH);
-    if (rc != TRIMUL_OK) return rc;
-    e = trimul::launch_tri_contract_pair(tmA, tmBh, out_maps, a, num_sms_current(), stream);
-  } else {
-    e = trimul::launch_tri_contract(tmA, tmB, out_maps, a, num_sms_current(), stream);
-  }
-  if (e != cudaSuccess) return cuda_fail(e, "tri_contract launch");
-  return TRIMUL_OK;
+  ContractPart part;
+  rc = build_contract(geom, d, tuning, ab_local, tri_peers, status, nullptr, timeout_ns, num_sms_current(), &part);
+  if (rc != TRIMUL_OK) return rc;
+  return launch_contract(part, num_sms_current(), stream);
 }
 
 int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, const void* gate, const void* w_fold,
@@ -474,50 +580,10 @@ int trimul_sm100_ln_out_proj(const trimul_geom_t* geom, const void* tri_local, c
   Derived d;
   int rc = check_geom(geom, &d);
   if (rc != TRIMUL_OK) return rc;
-  if (!tri_local || !gate || !w_fold || !cd || !out)
-    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ln_out_proj: NULL pointer");
-  const int D = geom->d;
-  CUtensorMap tmW, tmT;
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(D)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
-    rc = make_tmap(&tmW, w_fold, 2, dims, strides, box);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  {
-    // tri as (tokens contiguous, channels): the tile is consumed token-major exactly as stored
-    const uint64_t dims[2] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(D)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(d.rows) * 2};
-    const uint32_t box[2] = {64, 64};
-    rc = make_tmap(&tmT, tri_local, 2, dims, strides, box);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  CUtensorMap tmG, tmO;
-  {
-    // gate and out, token-major (rows, D): boxes of 64 channels x 128 tokens (128-byte rows)
-    const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(d.rows)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, 128};
-    rc = make_tmap(&tmG, gate, 2, dims, strides, box);
-    if (rc != TRIMUL_OK) return rc;
-    rc = make_tmap(&tmO, out, 2, dims, strides, box);
-    if (rc != TRIMUL_OK) return rc;
-  }
-  trimul::OutProjArgs a;
-  memset(&a, 0, sizeof(a));
-  a.gate = gate;
-  a.cd = cd;
-  a.out = out;
-  a.eps = geom->eps;
-  a.D = D;
-  a.rows = d.rows;
-  a.debug_skip = (debug_skip_bits() >> 4) & 15;
-  a.status = reinterpret_cast<trimul::DeviceStatus*>(status);
-  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-  cudaError_t e = trimul::launch_out_proj(tmW, tmT, tmG, tmO, a, num_sms_current(), stream);
-  if (e != cudaSuccess) return cuda_fail(e, "ln_out_proj launch");
-  return TRIMUL_OK;
+  OutPart part;
+  rc = build_out(geom, d, tri_local, gate, w_fold, cd, status, nullptr, timeout_ns, &part);
+  if (rc != TRIMUL_OK) return rc;
+  return launch_out(part, out, num_sms_current(), stream);
 }
 
 int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
@@ -530,12 +596,63 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "trimul_sm100_forward is the single-GPU chain; cp grid must be 1 x 1");
   void* ab_peers[1] = {ab};
   void* tri_peers[1] = {tri};
-  int rc = trimul_sm100_ln_gated_proj(geom, x, mask, mask_kind, ln_in_w, ln_in_b, w_packed, bias_packed, ab_peers,
-                                      gate, status, timeout_ns, stream);
+  int rc = trimul_sm100_ln_gated_proj(geom, nullptr, x, mask, mask_kind, ln_in_w, ln_in_b, w_packed, bias_packed,
+                                      ab_peers, gate, status, timeout_ns, stream);
   if (rc != TRIMUL_OK) return rc;
-  rc = trimul_sm100_tri_contract(geom, ab, tri_peers, status, timeout_ns, stream);
+  rc = trimul_sm100_tri_contract(geom, nullptr, ab, tri_peers, status, timeout_ns, stream);
   if (rc != TRIMUL_OK) return rc;
   return trimul_sm100_ln_out_proj(geom, tri, gate, w_fold, cd, out, status, timeout_ns, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// plans: the three launches of one (geometry, buffers) binding with every descriptor encoded once
+// ---------------------------------------------------------------------------------------------
+int trimul_sm100_plan_create(const trimul_plan_desc_t* desc, trimul_plan_t** out) {
+  if (desc == nullptr || out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan_create: NULL argument");
+  *out = nullptr;
+  Derived d;
+  int rc = check_geom(&desc->geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  const int sms = num_sms_current();
+  if (sms <= 0) return fail(TRIMUL_ERR_CUDA, "plan_create: cannot query the current device");
+  trimul_plan* pl = new (std::nothrow) trimul_plan;
+  if (pl == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan_create: out of host memory");
+  pl->num_sms = sms;
+  cudaGetDevice(&pl->device);
+  void* const* abp = desc->ab_peers;
+  void* const* trp = desc->tri_peers;
+  rc = build_front(&desc->geom, d, &desc->tuning, desc->ln_in_w, desc->ln_in_b, desc->w_packed, desc->bias_packed, abp,
+                   desc->gate, desc->status, desc->timeline, desc->timeout_ns, &pl->front);
+  if (rc == TRIMUL_OK)
+    rc = build_contract(&desc->geom, d, &desc->tuning, desc->ab_peers[desc->geom.rank], trp, desc->status, desc->timeline,
+                        desc->timeout_ns, sms, &pl->contract);
+  if (rc == TRIMUL_OK)
+    rc = build_out(&desc->geom, d, desc->tri_peers[desc->geom.rank], desc->gate, desc->w_fold, desc->cd, desc->status,
+                   desc->timeline, desc->timeout_ns, &pl->out);
+  if (rc != TRIMUL_OK) {
+    delete pl;
+    return rc;
+  }
+  *out = pl;
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_plan_ln_gated_proj(trimul_plan_t* plan, const void* x, const void* mask, int32_t mask_kind,
+                                    trimul_stream_t stream) {
+  if (plan == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan is NULL");
+  return launch_front(plan->front, x, mask, mask_kind, plan->num_sms, stream);
+}
+
+int trimul_sm100_plan_tri_contract(trimul_plan_t* plan, trimul_stream_t stream) {
+  if (plan == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan is NULL");
+  return launch_contract(plan->contract, plan->num_sms, stream);
+}
+
+int trimul_sm100_plan_ln_out_proj(trimul_plan_t* plan, void* out, trimul_stream_t stream) {
+  if (plan == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan is NULL");
+  return launch_out(plan->out, out, plan->num_sms, stream);
+}
+
+void trimul_sm100_plan_destroy(trimul_plan_t* plan) { delete plan; }
 
 }  // extern "C"

@@ -35,6 +35,29 @@ __device__ __forceinline__ void report_timeout(DeviceStatus* st, int kernel, int
   }
 }
 
+// Optional device timeline of one forward: sixteen %globaltimer values (ns) per rank.  "First"
+// slots are reduced with atomicMin over the CTAs of a kernel (the host presets them to all ones),
+// "last" slots with atomicMax (preset 0); the flag waits write their entry and exit times.  One
+// atomic per CTA per slot: free next to a kernel's run time.  A null pointer switches it off.
+enum TimelineSlot : int {
+  kTlFrontStart = 0,        // min: projection kernel, first CTA running
+  kTlFrontFirstStore = 1,   // min: first a|b store issued (local or peer)
+  kTlFrontLastStore = 2,    // max: last store of the kernel performed
+  kTlContractStart = 3,     // min
+  kTlContractLastStore = 4, // max
+  kTlOutStart = 5,          // min
+  kTlOutEnd = 6,            // max
+  kTlWaitBase = 8,          // + 2 * flag slot: wait entry, + 1: wait exit (FRONT, BACK, CONSUMED)
+  kTlSlots = 16,
+};
+
+__device__ __forceinline__ void timeline_min(unsigned long long* tl, int slot) {
+  if (tl != nullptr) atomicMin(tl + slot, static_cast<unsigned long long>(sm100::globaltimer_ns()));
+}
+__device__ __forceinline__ void timeline_max(unsigned long long* tl, int slot) {
+  if (tl != nullptr) atomicMax(tl + slot, static_cast<unsigned long long>(sm100::globaltimer_ns()));
+}
+
 // Base pointers of one logical buffer on every rank of the cp group (index = flat cp rank).
 // At cp=1 only ptr[0] is used and it is local memory.
 struct PeerPtrs {

@@ -42,13 +42,14 @@ struct GatedProjArgs {
   int dst_x0, dst_y0;    // the same origin as tensor-map coordinates: dst_base = dst_y0 * dst_line + dst_x0
   int gate_walk_dim;     // which coordinate of the gate map the walk index is (1 or 2; the line index is the other)
   void* gate_out;        // bf16 (rows, D): sigmoid(xn * g_out^T + b), local, row index as x
-  int debug_skip;        // profiling aid (TRIMUL_DEBUG_SKIP): bit0 skip a|b stores, bit1 skip gate stores, bit2 skip x loads
+  int rotate_chunks;     // 1: CTAs start the gated chunks at different points of the cycle (spreads the stores over the owners)
+  unsigned long long* timeline;  // optional device timeline (TimelineSlot), nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
 
 // Store-side tensor maps of the projection kernel.  ab[s]: rank s's operand buffer as
-// (x, y, batch, 2*D_loc planes), box 128 tokens x 16 planes, no swizzle; dim 0 is clipped at the end of
+// (x, y, batch, 2*D_loc planes), box 64 tokens x 16 planes, 128-byte swizzle; dim 0 is clipped at the end of
 // this rank's walk so ragged tiles never touch a neighbour's tokens.  gate: the local gate buffer
 // as (D, walk | line, line | walk, batch), box 64 channels x 128 tokens, 128-byte swizzle.
 struct GatedOutMaps {
@@ -72,7 +73,7 @@ struct TriContractArgs {
   PeerPtrs out;
   int ni_loc, nj_loc, cp1;
   int chan_offset;
-  int direct_stores;  // diagnostic (TRIMUL_DEBUG_SKIP bit 9): skip the staged TMA stores, store from registers
+  unsigned long long* timeline;  // optional device timeline, nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;
 };
@@ -100,7 +101,7 @@ struct OutProjArgs {
   float eps;
   int D;
   long rows;
-  int debug_skip;        // profiling aid: bit1 skip gate loads, bit2 skip out stores, bit3 skip the epilogue math
+  unsigned long long* timeline;  // optional device timeline, nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;
 };

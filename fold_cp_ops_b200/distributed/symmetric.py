@@ -23,7 +23,7 @@ Every wait is a bounded device-side poll; nothing here blocks the host.
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -66,21 +66,25 @@ def symmetric_empty(shape: Sequence[int], dtype: torch.dtype, device: torch.devi
 class PeerFlags:
     """The three counters of one workspace and the enqueue helpers the engine calls."""
 
-    def __init__(self, flags: torch.Tensor, flag_ptrs: List[int], cp: int, status: torch.Tensor, timeout_ns: int):
+    def __init__(self, flags: torch.Tensor, flag_ptrs: List[int], cp: int, status: torch.Tensor, timeout_ns: int,
+                 timeline: Optional[torch.Tensor] = None):
         self.flags, self.flag_ptrs, self.cp = flags, flag_ptrs, cp
-        self.status, self.timeout_ns = status, timeout_ns
+        self.status, self.timeout_ns, self.timeline = status, timeout_ns, timeline
         self.epoch = 0
+
+    def _wait(self, slot: int, expected: int) -> None:
+        K.peer_wait(self.flags, slot, expected, self.status, self.timeout_ns, self.timeline)
 
     def front_done(self) -> None:
         self.epoch += 1
         K.peer_signal(self.flag_ptrs, SLOT_FRONT)
-        K.peer_wait(self.flags, SLOT_FRONT, self.cp * self.epoch, self.status, self.timeout_ns)
+        self._wait(SLOT_FRONT, self.cp * self.epoch)
         if self.epoch > 1:
-            K.peer_wait(self.flags, SLOT_CONSUMED, self.cp * (self.epoch - 1), self.status, self.timeout_ns)
+            self._wait(SLOT_CONSUMED, self.cp * (self.epoch - 1))
 
     def back_done(self) -> None:
         K.peer_signal(self.flag_ptrs, SLOT_BACK)
-        K.peer_wait(self.flags, SLOT_BACK, self.cp * self.epoch, self.status, self.timeout_ns)
+        self._wait(SLOT_BACK, self.cp * self.epoch)
 
     def consumed(self) -> None:
         K.peer_signal(self.flag_ptrs, SLOT_CONSUMED)
@@ -90,7 +94,7 @@ class SymmetricWorkspace:
     """Peer-mapped ``ab`` / ``tri`` buffers + flags for one ``(B, N)`` on one rank.  COLLECTIVE to build."""
 
     def __init__(self, group, device: torch.device, geometry, ab_shape, tri_shape, status: torch.Tensor = None,
-                 timeout_ns: int = K.DEFAULT_TIMEOUT_NS):
+                 timeout_ns: int = K.DEFAULT_TIMEOUT_NS, timeline: Optional[torch.Tensor] = None):
         self.group = group
         cp = geometry.cp
         if dist.get_world_size(group) != cp:
@@ -109,8 +113,8 @@ class SymmetricWorkspace:
         self._flag_ptrs = [flag_ptrs[i] for i in order]
         self.flags = None
         if status is not None:
-            self.bind(status, timeout_ns)
+            self.bind(status, timeout_ns, timeline)
 
-    def bind(self, status: torch.Tensor, timeout_ns: int) -> "SymmetricWorkspace":
-        self.flags = PeerFlags(self._flag_tensor, self._flag_ptrs, len(self._flag_ptrs), status, timeout_ns)
+    def bind(self, status: torch.Tensor, timeout_ns: int, timeline: Optional[torch.Tensor] = None) -> "SymmetricWorkspace":
+        self.flags = PeerFlags(self._flag_tensor, self._flag_ptrs, len(self._flag_ptrs), status, timeout_ns, timeline)
         return self

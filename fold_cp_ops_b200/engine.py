@@ -10,24 +10,45 @@ on the current CUDA stream.  There is no NCCL call, no host synchronisation and 
 all-to-all on that path: the two reshards are the kernels' own epilogue stores into the owning
 rank's buffer, and rank-to-rank ordering is a counter exchange done by two tiny flag kernels.
 At cp=1 the same kernels run with a one-entry peer table and no flag kernels at all.
+
+Every launch goes through a :class:`fold_cp_ops_b200.kernels.Plan` that is built once per
+``(B, N, direction)`` -- the TMA descriptors of a forward are encoded when the workspace is made,
+not on every call.
+
+A device-side wait that expires makes its kernel return early and leaves a status record.  The
+engine copies that record to pinned host memory after every forward; the NEXT forward (and
+:meth:`TriMulEngine.check`) raises :class:`DeviceWaitTimeout` when it finds one, so a caller of the
+public API cannot keep consuming outputs of a forward that gave up.
 """
 from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
+from . import _lib
 from . import kernels as K
 
-_LN_KEYS = ("norm_in_w", "norm_in_b", "norm_out_w", "norm_out_b")
 SUPPORTED_D = (128, 256)
 
+#: default bound of the cross-rank flag waits.  Much longer than the in-kernel pipeline waits (2 s):
+#: a peer whose HOST is late (data loading, checkpoint IO, garbage collection) must be waited for, as
+#: the reference's drains do; the bound only exists so that a dead peer cannot hang a shared GPU.
+DEFAULT_PEER_TIMEOUT_NS = 30_000_000_000
 
-def _timeout_ns() -> int:
-    ms = os.environ.get("CPO_A2A_WAIT_TIMEOUT_MS")
-    return int(float(ms) * 1e6) if ms else K.DEFAULT_TIMEOUT_NS
+#: measured defaults of the sm_100a kernels per (feature width, cp): form of the contraction kernel and
+#: whether the projection kernel's CTAs walk their gated chunks in rotated order.  CTA pairs won at
+#: every shape (27.5 vs 30.8 ms at N=4096 D=256, 3.13 vs 3.45 ms at N=2048); the rotation costs nothing
+#: at cp=1 and spreads the peer stores over all NVLink directions at cp>1 (cp=2: 9.1-9.4 vs 9.7-10.3 ms).
+SM100_DEFAULTS = {(d, cp): {"contract_form": "pair", "front_fixed_order": False}
+                  for d in SUPPORTED_D for cp in (1, 2, 4, 8)}
+
+
+def _env_ms(name: str) -> Optional[int]:
+    v = os.environ.get(name)
+    return int(float(v) * 1e6) if v else None
 
 
 @dataclass
@@ -83,10 +104,15 @@ class TriMulEngine:
     ``forward(x_local, direction, mask_local)`` takes this rank's ``(B, N/cp0, N/cp1, D)`` block
     and returns the same block of the output, freshly allocated, bf16.  Workspaces are cached per
     ``(B, N)``; at cp > 1 they are symmetric allocations exchanged once with the peers.
+
+    Tuning (all optional): ``contract_form`` ``"auto" | "single" | "pair"``, ``front_fixed_order``,
+    ``wait_timeout_ms`` (bound of the cross-rank flag waits; ``CPO_A2A_WAIT_TIMEOUT_MS`` overrides).
     """
 
     def __init__(self, w: Dict[str, Optional[torch.Tensor]], *, device: torch.device, eps: float = 1e-5,
-                 geometry: Optional[CpGeometry] = None, process_group=None, recv_cache: Optional[int] = None):
+                 geometry: Optional[CpGeometry] = None, process_group=None, recv_cache: Optional[int] = None,
+                 contract_form: Optional[str] = None, front_fixed_order: Optional[bool] = None,
+                 wait_timeout_ms: Optional[float] = None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("TriMulEngine needs a CUDA device: the TriMul kernels have no CPU path")
@@ -99,14 +125,24 @@ class TriMulEngine:
         self.group = process_group
         if self.geometry.cp > 1 and process_group is None:
             raise ValueError("a cp > 1 engine needs the process group of its cp peers")
+        defaults = SM100_DEFAULTS.get((self.D, self.geometry.cp), {"contract_form": "auto", "front_fixed_order": False})
+        self.contract_form = contract_form if contract_form is not None else defaults["contract_form"]
+        self.front_fixed_order = bool(defaults["front_fixed_order"] if front_fixed_order is None else front_fixed_order)
+        self.tuning = K.make_tuning(self.contract_form, self.front_fixed_order)
         self.status = K.new_status(self.device)
-        self.timeout_ns = _timeout_ns()
+        self._status_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self._status_event: Optional[torch.cuda.Event] = None
+        self.timeout_ns = K.DEFAULT_TIMEOUT_NS
+        env_wait = _env_ms("CPO_A2A_WAIT_TIMEOUT_MS")
+        self.peer_timeout_ns = env_wait or (int(wait_timeout_ms * 1e6) if wait_timeout_ms else DEFAULT_PEER_TIMEOUT_NS)
         cap = os.environ.get("CPO_TRIMUL_RECV_CACHE")
         self._cache_cap = int(cap) if cap else (recv_cache if recv_cache is not None else 2)
         self._ws: Dict[Tuple[int, int], "_Workspace"] = {}
-        self._epoch = 0
         self.stage_log = bool(int(os.environ.get("CPO_TRIMUL_STAGE_LOG", "0") or 0))
+        self.collect_stats = self.stage_log
         self.last_stage_ms: Dict[str, float] = {}
+        self._last_stats: Dict[str, object] = {}
+        self._stats_ws: Optional["_Workspace"] = None
 
     # ------------------------------------------------------------------------------------------
     def _check_shapes(self, x_local: torch.Tensor, N: int) -> None:
@@ -129,7 +165,7 @@ class TriMulEngine:
         ws = self._ws.get(key)
         if ws is None:
             while len(self._ws) >= max(1, self._cache_cap):
-                self._ws.pop(next(iter(self._ws)))  # FIFO; buffers return to their pool by refcount
+                self._ws.pop(next(iter(self._ws))).close()  # FIFO; buffers return to their pool by refcount
             ws = _Workspace(self, B, N)
             self._ws[key] = ws
         return ws
@@ -151,6 +187,7 @@ class TriMulEngine:
         self._check_shapes(x_local, N)
         if x_local.device != self.device:
             raise ValueError(f"x_local is on {x_local.device}, the engine on {self.device}")
+        self._raise_if_previous_forward_gave_up()
         x = x_local if x_local.dtype is torch.bfloat16 else x_local.to(torch.bfloat16)
         x = x.contiguous()
         mask = None
@@ -165,21 +202,65 @@ class TriMulEngine:
             ws = self._workspace(B, N)
             out = torch.empty_like(x)
             ws.run(x, mask, direction, out)
+            # mirror the status record to the host: read by the next forward / check() without a sync
+            self._status_host.copy_(self.status, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._status_event = ev
         return out
 
+    # ------------------------------------------------------------------------------------------
+    def _raise_from(self, record) -> None:
+        self.status.zero_()
+        self._status_host.zero_()
+        self._status_event = None
+        raise K.DeviceWaitTimeout(K.describe_status(record))
+
+    def _raise_if_previous_forward_gave_up(self) -> None:
+        """Non-blocking: looks at the host mirror of the status record if its copy has finished."""
+        ev = self._status_event
+        if ev is not None and ev.query():
+            rec = self._status_host.tolist()
+            if rec[0] != 0:
+                self._raise_from(rec)
+
     def check(self) -> None:
-        """Synchronising check of the device status record (raises on an expired wait)."""
-        K.check_status(self.status)
+        """Synchronising check of the device status record: raises :class:`DeviceWaitTimeout` if any
+        bounded wait of a forward issued so far expired (that forward's output is invalid)."""
+        rec = self.status.tolist()
+        if rec[0] != 0:
+            self._raise_from(rec)
+
+    def last_forward_stats(self) -> Dict[str, object]:
+        """Measurements of the most recent forward made with ``collect_stats = True`` (synchronises).
+
+        ``stage_ms``: CUDA-event time of the three kernels alone (the flag kernels are outside these
+        windows); ``wait_ms``: time this rank's stream sat in each cross-rank flag wait, from the
+        device timeline (the all-to-all time that was NOT hidden behind a kernel); ``span_ms``:
+        first-CTA-start to last-store of each kernel on the device clock; ``bytes_to_peers``: bytes
+        this rank's epilogues stored into other ranks' buffers."""
+        ws = self._stats_ws
+        if ws is None:
+            return dict(self._last_stats)
+        self._last_stats = ws.collect()
+        self._stats_ws = None
+        return dict(self._last_stats)
 
     def free(self) -> None:
         """Drop the cached workspaces.  Symmetric blocks go back to their pool by refcount; no
         collective runs here, so ranks may call this in any order."""
+        for ws in self._ws.values():
+            ws.close()
         self._ws.clear()
 
 
+_TL_FIRST = (_lib.TL_FRONT_START, _lib.TL_FRONT_FIRST_STORE, _lib.TL_CONTRACT_START, _lib.TL_OUT_START)
+
+
 class _Workspace:
-    """Buffers for one ``(B, N)``.  cp=1: plain allocations, optionally one batch plane at a time
-    when the full-batch operand buffer would not fit; cp>1: symmetric allocations + flag pads."""
+    """Buffers and launch plans for one ``(B, N)``.  cp=1: plain allocations, optionally one batch
+    plane at a time when the full-batch operand buffer would not fit; cp>1: symmetric allocations +
+    flag pads."""
 
     def __init__(self, eng: TriMulEngine, B: int, N: int):
         self.eng, self.B, self.N = eng, B, N
@@ -188,6 +269,10 @@ class _Workspace:
         dev = eng.device
         self.ni, self.nj = N // g.cp0, N // g.cp1
         self.planes_b = B  # batch planes handled per kernel launch
+        self.timeline = torch.zeros(_lib.TIMELINE_SLOTS, dtype=torch.int64, device=dev)
+        preset = torch.zeros(_lib.TIMELINE_SLOTS, dtype=torch.int64)
+        preset[list(_TL_FIRST)] = -1  # all ones: the identity of an unsigned min
+        self._tl_preset = preset.to(dev)
         if g.cp == 1:
             geom = K.make_geom(B, N, D, "outgoing", eng.eps)
             need = K.workspace_bytes(geom)
@@ -209,43 +294,90 @@ class _Workspace:
             d_loc = D // g.cp
             self.sym = symmetric.SymmetricWorkspace(
                 eng.group, dev, g, ab_shape=(2, d_loc, B, N, N), tri_shape=(D, B, self.ni, self.nj),
-                status=eng.status, timeout_ns=eng.timeout_ns)
+                status=eng.status, timeout_ns=eng.peer_timeout_ns, timeline=self.timeline)
             self.ab, self.tri = self.sym.ab, self.sym.tri
             self.ab_ptrs, self.tri_ptrs = self.sym.ab_ptrs, self.sym.tri_ptrs
             self.gate = torch.empty((B, self.ni, self.nj, D), dtype=torch.bfloat16, device=dev)
             self.flags = self.sym.flags
+        self._plans: Dict[str, K.Plan] = {}
+        self._events = None
+
+    def _plan(self, direction: str) -> K.Plan:
+        plan = self._plans.get(direction)
+        if plan is None:
+            eng, g = self.eng, self.eng.geometry
+            geom = K.make_geom(self.planes_b, self.N, eng.D, direction, eng.eps, g.cp0, g.cp1, g.rank)
+            plan = K.Plan(geom, eng.weights, self.ab_ptrs, self.tri_ptrs, self.gate, eng.status,
+                          timeline=self.timeline, timeout_ns=eng.timeout_ns, tuning=eng.tuning)
+            self._plans[direction] = plan
+        return plan
+
+    def close(self) -> None:
+        for plan in self._plans.values():
+            plan.close()
+        self._plans.clear()
 
     def run(self, x, mask, direction, out) -> None:
         eng = self.eng
-        g = eng.geometry
-        W = eng.weights
         pb = self.planes_b
-        log = eng.stage_log
+        stats = eng.collect_stats or eng.stage_log
+        plan = self._plan(direction)
         for b0 in range(0, self.B, pb):
             xs = x[b0:b0 + pb]
             ms = None if mask is None else mask.reshape(self.B, self.ni, self.nj)[b0:b0 + pb]
             os_ = out[b0:b0 + pb]
-            geom = K.make_geom(pb, self.N, eng.D, direction, eng.eps, g.cp0, g.cp1, g.rank)
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if log else None
-            if log:
+            ev = None
+            if stats:
+                self.timeline.copy_(self._tl_preset)
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
                 ev[0].record()
-            K.ln_gated_proj(geom, xs, ms, W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed, self.ab_ptrs, self.gate,
-                            eng.status, eng.timeout_ns)
+            plan.ln_gated_proj(xs, ms)
+            if stats:
+                ev[1].record()
             if self.flags is not None:
                 self.flags.front_done()
-            if log:
-                ev[1].record()
-            K.tri_contract(geom, self.ab, self.tri_ptrs, eng.status, eng.timeout_ns)
+            if stats:
+                ev[2].record()
+            plan.tri_contract()
+            if stats:
+                ev[3].record()
             if self.flags is not None:
                 self.flags.back_done()
-            if log:
-                ev[2].record()
-            K.ln_out_proj(geom, self.tri, self.gate, W.w_fold, W.cd, os_, eng.status, eng.timeout_ns)
+            if stats:
+                ev[4].record()
+            plan.ln_out_proj(os_)
+            if stats:
+                ev[5].record()
             if self.flags is not None:
                 self.flags.consumed()
-            if log:
-                ev[3].record()
-                ev[3].synchronize()
-                eng.last_stage_ms = {"ln_gated_proj": ev[0].elapsed_time(ev[1]), "tri_contract": ev[1].elapsed_time(ev[2]),
-                                     "ln_out_proj": ev[2].elapsed_time(ev[3])}
-                print(f"[trimul stage log] {eng.last_stage_ms}", flush=True)
+            if stats:
+                self._events = ev
+                eng._stats_ws = self
+                if eng.stage_log:
+                    eng.last_forward_stats()
+                    print(f"[trimul stage log] {eng.last_stage_ms}", flush=True)
+
+    def collect(self) -> Dict[str, object]:
+        """Read the events and the device timeline of the last traced pass (synchronises)."""
+        eng, g = self.eng, self.eng.geometry
+        ev = self._events
+        ev[5].synchronize()
+        stage = {"ln_gated_proj": ev[0].elapsed_time(ev[1]), "tri_contract": ev[2].elapsed_time(ev[3]),
+                 "ln_out_proj": ev[4].elapsed_time(ev[5])}
+        eng.last_stage_ms = stage
+        tl = self.timeline.tolist()
+        ms = lambda a, b: (tl[b] - tl[a]) * 1e-6 if tl[a] > 0 and tl[b] > 0 else None
+        base = _lib.TL_WAIT_BASE
+        wait = {}
+        if g.cp > 1:
+            wait = {"front": ms(base + 0, base + 1), "back": ms(base + 2, base + 3), "consumed": ms(base + 4, base + 5)}
+        span = {"ln_gated_proj": ms(_lib.TL_FRONT_START, _lib.TL_FRONT_LAST_STORE),
+                "first_store_after_start": ms(_lib.TL_FRONT_START, _lib.TL_FRONT_FIRST_STORE),
+                "tri_contract": ms(_lib.TL_CONTRACT_START, _lib.TL_CONTRACT_LAST_STORE),
+                "ln_out_proj": ms(_lib.TL_OUT_START, _lib.TL_OUT_END),
+                "forward": ms(_lib.TL_FRONT_START, _lib.TL_OUT_END)}
+        s = self.planes_b * self.ni * self.nj * eng.D * 2  # bytes of one local activation
+        peers = g.cp - 1
+        return {"stage_ms": stage, "wait_ms": wait, "span_ms": span,
+                "step_ms": ev[0].elapsed_time(ev[5]),
+                "bytes_to_peers": {"front": 2 * s * peers // g.cp, "back": s * peers // g.cp}}

@@ -12,6 +12,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
+from .distributed.collective_symmetry import CollectiveError
 
 DEFAULT_TIMEOUT_NS = 2_000_000_000
 
@@ -72,11 +73,25 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros(8, dtype=torch.int32, device=device)
 
 
-class DeviceWaitTimeout(RuntimeError):
-    """A bounded device-side wait expired; the kernel returned early and the context is intact."""
+class DeviceWaitTimeout(CollectiveError):
+    """A bounded device-side wait expired; the kernel returned early and the CUDA context is intact.
+
+    A member of the ``CollectiveError`` family: the usual cause is a peer rank that never delivered
+    its half of a reshard, and the right reaction is the same -- do not enter another collective
+    with outputs of this forward."""
 
 
 _KERNEL_NAMES = {1: "ln_gated_proj", 2: "tri_contract", 3: "ln_out_proj", 4: "peer_sync"}
+
+
+def describe_status(record: Sequence[int]) -> str:
+    """The sentence a status record (8 x int32 as a list) stands for."""
+    if record[1] == 4:
+        slot = {0: "FRONT", 1: "BACK", 2: "CONSUMED"}.get(record[3], str(record[3]))
+        return (f"a cross-rank flag wait expired: counter {slot} stood at {record[4]} when the bound ran out -- a "
+                "peer rank did not deliver its half of a reshard; outputs of this forward are invalid")
+    return (f"bounded wait expired in kernel {_KERNEL_NAMES.get(record[1], record[1])}: block {record[2]}, role "
+            f"{record[3]}, detail {record[4]}; outputs of this forward are invalid")
 
 
 def check_status(status: torch.Tensor) -> None:
@@ -84,10 +99,7 @@ def check_status(status: torch.Tensor) -> None:
     s = status.tolist()
     if s[0] != 0:
         status.zero_()
-        raise DeviceWaitTimeout(
-            f"bounded wait expired in kernel {_KERNEL_NAMES.get(s[1], s[1])}: block {s[2]}, role {s[3]}, "
-            f"detail {s[4]}; outputs of this forward are invalid"
-        )
+        raise DeviceWaitTimeout(describe_status(s))
 
 
 def pack_weights(d: int, p_in_w, g_in_w, g_out_w, p_in_b=None, g_in_b=None, g_out_b=None):
@@ -128,23 +140,40 @@ def _ptr_array(ptrs: Sequence[int]):
     return arr
 
 
+def make_tuning(contract_form: str = "auto", front_fixed_order: bool = False) -> _lib.Tuning:
+    """The library's tuning record: ``contract_form`` is ``"auto"`` (CTA pairs whenever the device has two
+    SMs), ``"single"`` (one CTA per 128 x 256 tile) or ``"pair"`` (two CTAs per 256 x 256 tile)."""
+    forms = {"auto": _lib.CONTRACT_DEFAULT, "single": _lib.CONTRACT_SINGLE, "pair": _lib.CONTRACT_PAIR}
+    if contract_form not in forms:
+        raise ValueError(f"contract_form must be one of {sorted(forms)}; got {contract_form!r}")
+    t = _lib.Tuning()
+    t.contract_form = forms[contract_form]
+    t.front_fixed_order = 1 if front_fixed_order else 0
+    return t
+
+
+def _tuning_ref(tuning):
+    return None if tuning is None else C.byref(tuning)
+
+
 def ln_gated_proj(geom, x, mask, ln_w, ln_b, w_packed, bias_packed, ab_peer_ptrs: Sequence[int], gate_out,
-                  status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+                  status, timeout_ns: int = DEFAULT_TIMEOUT_NS, tuning=None) -> None:
     _require(x, torch.bfloat16, "x")
     _require(ln_w, torch.float32, "ln_w")
     if ln_b is not None:
         _require(ln_b, torch.float32, "ln_b")
     _require(gate_out, torch.bfloat16, "gate_out")
     mptr, mkind = _mask_args(mask)
-    rc = _lib.load().trimul_sm100_ln_gated_proj(C.byref(geom), _ptr(x), mptr, mkind, _ptr(ln_w), _ptr(ln_b),
+    rc = _lib.load().trimul_sm100_ln_gated_proj(C.byref(geom), _tuning_ref(tuning), _ptr(x), mptr, mkind, _ptr(ln_w), _ptr(ln_b),
                                                 _ptr(w_packed), _ptr(bias_packed), _ptr_array(ab_peer_ptrs),
                                                 _ptr(gate_out), _ptr(status), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_ln_gated_proj")
 
 
-def tri_contract(geom, ab_local, tri_peer_ptrs: Sequence[int], status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+def tri_contract(geom, ab_local, tri_peer_ptrs: Sequence[int], status, timeout_ns: int = DEFAULT_TIMEOUT_NS,
+                 tuning=None) -> None:
     _require(ab_local, torch.bfloat16, "ab_local")
-    rc = _lib.load().trimul_sm100_tri_contract(C.byref(geom), _ptr(ab_local), _ptr_array(tri_peer_ptrs),
+    rc = _lib.load().trimul_sm100_tri_contract(C.byref(geom), _tuning_ref(tuning), _ptr(ab_local), _ptr_array(tri_peer_ptrs),
                                                _ptr(status), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_tri_contract")
 
@@ -215,8 +244,60 @@ def peer_signal(flag_peer_ptrs: Sequence[int], slot: int) -> None:
     _lib.check(rc, "trimul_sm100_peer_signal")
 
 
-def peer_wait(local_flags: torch.Tensor, slot: int, expected: int, status, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+def peer_wait(local_flags: torch.Tensor, slot: int, expected: int, status, timeout_ns: int = DEFAULT_TIMEOUT_NS,
+              timeline: Optional[torch.Tensor] = None) -> None:
     """Hold the current stream until this rank's counter ``slot`` reaches ``expected`` (bounded)."""
     rc = _lib.load().trimul_sm100_peer_wait(_ptr(local_flags), int(slot), int(expected), _ptr(status),
-                                            int(timeout_ns), _stream())
+                                            _ptr(timeline), int(timeout_ns), _stream())
     _lib.check(rc, "trimul_sm100_peer_wait")
+
+
+class Plan:
+    """One rank's three launches for a fixed geometry and set of buffers (``trimul_plan_t``): every TMA
+    descriptor is encoded once here instead of on every forward.  Holds references to the tensors whose
+    addresses it captured; ``close()`` (or garbage collection) releases the host object."""
+
+    def __init__(self, geom, weights, ab_peer_ptrs: Sequence[int], tri_peer_ptrs: Sequence[int], gate: torch.Tensor,
+                 status: torch.Tensor, *, timeline: Optional[torch.Tensor] = None, timeout_ns: int = DEFAULT_TIMEOUT_NS,
+                 tuning=None):
+        _require(gate, torch.bfloat16, "gate")
+        d = _lib.PlanDesc()
+        d.geom = geom
+        d.tuning = tuning if tuning is not None else _lib.Tuning()
+        d.ln_in_w, d.ln_in_b = _ptr(weights.norm_in_w), _ptr(weights.norm_in_b)
+        d.w_packed, d.bias_packed = _ptr(weights.w_packed), _ptr(weights.bias_packed)
+        d.w_fold, d.cd = _ptr(weights.w_fold), _ptr(weights.cd)
+        for i, p in enumerate(ab_peer_ptrs):
+            d.ab_peers[i] = int(p)
+        for i, p in enumerate(tri_peer_ptrs):
+            d.tri_peers[i] = int(p)
+        d.gate, d.status, d.timeline, d.timeout_ns = _ptr(gate), _ptr(status), _ptr(timeline), int(timeout_ns)
+        self._keep = (weights, gate, status, timeline)
+        handle = C.c_void_p()
+        _lib.check(_lib.load().trimul_sm100_plan_create(C.byref(d), C.byref(handle)), "trimul_sm100_plan_create")
+        self._h = handle
+
+    def ln_gated_proj(self, x: torch.Tensor, mask: Optional[torch.Tensor]) -> None:
+        _require(x, torch.bfloat16, "x")
+        mptr, mkind = _mask_args(mask)
+        _lib.check(_lib.load().trimul_sm100_plan_ln_gated_proj(self._h, _ptr(x), mptr, mkind, _stream()),
+                   "trimul_sm100_plan_ln_gated_proj")
+
+    def tri_contract(self) -> None:
+        _lib.check(_lib.load().trimul_sm100_plan_tri_contract(self._h, _stream()), "trimul_sm100_plan_tri_contract")
+
+    def ln_out_proj(self, out: torch.Tensor) -> None:
+        _require(out, torch.bfloat16, "out")
+        _lib.check(_lib.load().trimul_sm100_plan_ln_out_proj(self._h, _ptr(out), _stream()),
+                   "trimul_sm100_plan_ln_out_proj")
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            _lib.load().trimul_sm100_plan_destroy(self._h)
+        self._h = None
+
+    def __del__(self):  # pragma: no cover - interpreter teardown order
+        try:
+            self.close()
+        except Exception:
+            pass

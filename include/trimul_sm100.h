@@ -8,8 +8,9 @@
  *
  * Conventions
  *   - every function returns 0 on success or a negative TRIMUL_ERR_* code; nothing throws or exits;
- *   - every pointer is caller-owned DEVICE memory unless stated otherwise; nothing is allocated or
- *     freed here and there are no hidden streams: work is enqueued on the stream that is passed;
+ *   - every pointer is caller-owned DEVICE memory unless stated otherwise; no device memory is
+ *     allocated or freed here (a plan is a small HOST object) and there are no hidden streams: work
+ *     is enqueued on the stream that is passed;
  *   - all activations and weights are bf16, LayerNorm gains/biases and projection biases are fp32;
  *   - device-side waits are bounded: on expiry a kernel writes a trimul_status_t record and returns
  *     normally, so the CUDA context stays usable.  The caller owns the status record (8 x int32,
@@ -77,6 +78,34 @@ typedef struct trimul_status {
   int32_t pad[3];
 } trimul_status_t;
 
+/* Choices the sm_100a kernels leave open (0 in every field = the library's default).  Takes over the
+ * typed knobs of `TriMulTuning` (fold_cp_ops/distributed/workflows/trimul_tuning.py:72-217), whose SM90
+ * tile / cluster / drain settings have no meaning here. */
+#define TRIMUL_CONTRACT_DEFAULT 0 /* CTA pairs when the device has at least two SMs */
+#define TRIMUL_CONTRACT_SINGLE 1  /* one CTA per 128 x 256 output tile (tcgen05 cta_group::1) */
+#define TRIMUL_CONTRACT_PAIR 2    /* two CTAs per 256 x 256 output tile (tcgen05 cta_group::2) */
+typedef struct trimul_tuning {
+  int32_t contract_form;     /* TRIMUL_CONTRACT_* */
+  int32_t front_fixed_order; /* 1: every CTA of the projection kernel walks the gated chunks in the same
+                                order; 0: CTAs start at different chunks so that, at cp > 1, the grid's
+                                stores reach all owner ranks at any moment */
+  int32_t reserved[6];
+} trimul_tuning_t;
+
+/* Optional device timeline of one forward: TRIMUL_TIMELINE_SLOTS x uint64 of %globaltimer (ns) on this
+ * rank.  "first" slots are reduced with min over a kernel's CTAs -- preset them to UINT64_MAX -- and
+ * "last" slots with max -- preset 0; a flag wait writes its entry and exit time.  Time spent in the
+ * waits (exit - entry) is the all-to-all time this rank did NOT hide behind a kernel. */
+#define TRIMUL_TIMELINE_SLOTS 16
+#define TRIMUL_TL_FRONT_START 0        /* first: projection kernel running */
+#define TRIMUL_TL_FRONT_FIRST_STORE 1  /* first: first a|b store issued */
+#define TRIMUL_TL_FRONT_LAST_STORE 2   /* last: every store of the projection kernel performed */
+#define TRIMUL_TL_CONTRACT_START 3     /* first */
+#define TRIMUL_TL_CONTRACT_LAST_STORE 4 /* last */
+#define TRIMUL_TL_OUT_START 5          /* first */
+#define TRIMUL_TL_OUT_END 6            /* last */
+#define TRIMUL_TL_WAIT_BASE 8          /* + 2 * flag slot: wait entry; + 1: wait exit (flag slots 0..2) */
+
 /* Bytes of each buffer a rank needs for `geom` (all bf16):
  *   ab   : operand planes this rank contracts, (2, d/cp, batch, n, n)   -- written by every rank
  *   tri  : contraction result for this rank's tokens, (d, batch, n/cp0, n/cp1) -- written by every rank
@@ -136,17 +165,18 @@ int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w,
  * Replaces `layernorm_fwd` (fold_cp_ops/kernels/layernorm.py:730) + `DualGatedGemmDistStore.run`
  * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:1744) + the g_out half of
  * `layernorm_dual_gated_gemm` (fold_cp_ops/kernels/layernorm_dual_gated_gemm.py:5342). */
-int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
-                               const float* ln_w, const float* ln_b, const void* w_packed,
-                               const float* bias_packed, void* const* ab_peers, void* gate_out,
+int trimul_sm100_ln_gated_proj(const trimul_geom_t* geom, const trimul_tuning_t* tuning /* nullable */, const void* x,
+                               const void* mask, int32_t mask_kind, const float* ln_w, const float* ln_b,
+                               const void* w_packed, const float* bias_packed, void* const* ab_peers, void* gate_out,
                                trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
 
 /* Stage 3: per-channel n x n x n contraction of this rank's `ab` planes, back reshard fused in the
  * store.  tri_peers[s]: base of rank s's `tri` buffer.
  * Replaces `GemmA2AStore.run` (fold_cp_ops/distributed/workflows/trimul_autotuned.py:2548) and the
  * cp=1 `_gemm1` (fold_cp_ops/workflows/trimul_autotune.py:805). */
-int trimul_sm100_tri_contract(const trimul_geom_t* geom, const void* ab_local, void* const* tri_peers,
-                              trimul_status_t* status, uint64_t timeout_ns, trimul_stream_t stream);
+int trimul_sm100_tri_contract(const trimul_geom_t* geom, const trimul_tuning_t* tuning /* nullable */,
+                              const void* ab_local, void* const* tri_peers, trimul_status_t* status,
+                              uint64_t timeout_ns, trimul_stream_t stream);
 
 /* Fold the output LayerNorm into the output projection once at construction:
  *   w_fold[n,k] = bf16(ln_w[k] * w_out[n,k])            (d, d) bf16
@@ -171,6 +201,39 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
                          void* gate, void* out, trimul_status_t* status, uint64_t timeout_ns,
                          trimul_stream_t stream);
 
+/* A plan binds one geometry to one set of buffers and encodes every TMA descriptor of the three
+ * launches once (the stateless entry points above encode cp + 2, cp + 3 and 4 descriptors on every
+ * call).  It is a few KB of HOST memory; creating and destroying it touches no device memory.  Make the
+ * device the buffers live on current when creating it.  `ab_peers[geom.rank]` / `tri_peers[geom.rank]`
+ * are this rank's own buffers; `timeline` may be NULL.  The output descriptor is cached per `out`
+ * pointer.  Not thread-safe: one plan, one caller thread at a time.
+ * Takes over the construction half of `TriMulAutotuned.__init__` / `_rebind_runtime`
+ * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:2686-3244, 3553-3601), where the reference
+ * compiles its kernels and builds its per-peer store descriptors. */
+typedef struct trimul_plan trimul_plan_t;
+typedef struct trimul_plan_desc {
+  trimul_geom_t geom;
+  trimul_tuning_t tuning;
+  const float* ln_in_w;
+  const float* ln_in_b; /* nullable */
+  const void* w_packed;
+  const float* bias_packed; /* nullable */
+  const void* w_fold;
+  const float* cd;
+  void* ab_peers[TRIMUL_MAX_PEERS];
+  void* tri_peers[TRIMUL_MAX_PEERS];
+  void* gate;
+  trimul_status_t* status;
+  uint64_t* timeline; /* nullable; TRIMUL_TIMELINE_SLOTS x uint64 on the device */
+  uint64_t timeout_ns;
+} trimul_plan_desc_t;
+int trimul_sm100_plan_create(const trimul_plan_desc_t* desc, trimul_plan_t** out);
+int trimul_sm100_plan_ln_gated_proj(trimul_plan_t* plan, const void* x, const void* mask, int32_t mask_kind,
+                                    trimul_stream_t stream);
+int trimul_sm100_plan_tri_contract(trimul_plan_t* plan, trimul_stream_t stream);
+int trimul_sm100_plan_ln_out_proj(trimul_plan_t* plan, void* out, trimul_stream_t stream);
+void trimul_sm100_plan_destroy(trimul_plan_t* plan);
+
 /* Single-GPU forward for callers that cannot allocate device memory (no counterpart in the
  * reference, which always allocates its own buffers).  Same arguments as trimul_sm100_forward minus
  * the three scratch buffers: the a|b planes, the contraction result and the gate live in a
@@ -181,8 +244,11 @@ int trimul_sm100_forward(const trimul_geom_t* geom, const void* x, const void* m
  * 8 * batch * n * n * d <= TRIMUL_STATIC_SCRATCH_BYTES, otherwise TRIMUL_ERR_UNSUPPORTED_SHAPE with a
  * message in trimul_sm100_last_error().  All calls on a device share the one array: calls that overlap on
  * the GPU race.  The array keeps the previous call's contents; the forward overwrites everything it
- * reads, so nothing is cleared.  The first call on a device looks up the array's device address -- make
- * it outside any stream capture. */
+ * reads, so nothing is cleared.  The first call on a device looks up the array's device address (with
+ * that device current: the device that owns `stream` must be the current one) -- make it outside any
+ * stream capture.  The address is cached per device for the life of the process; a cudaDeviceReset
+ * invalidates it, after which this entry point must not be used again in that process.  Host threads
+ * may make their first calls concurrently. */
 #define TRIMUL_STATIC_SCRATCH_BYTES (32u << 20)
 int trimul_sm100_forward_static(const trimul_geom_t* geom, const void* x, const void* mask, int32_t mask_kind,
                                 const float* ln_in_w, const float* ln_in_b, const void* w_packed,
@@ -193,12 +259,13 @@ int trimul_sm100_forward_static(const trimul_geom_t* geom, const void* x, const 
  * counters (zeroed once).  `peer_signal` adds 1 to counter `slot` on every rank listed in
  * flag_peers[0..cp) (release, system scope) and is enqueued after the kernel whose stores it
  * publishes; `peer_wait` is enqueued before the kernel that consumes them and polls this rank's
- * own counter until it reaches `expected`, giving up after timeout_ns with a status record.
+ * own counter until it reaches `expected`, giving up after timeout_ns with a status record; with a
+ * timeline it records its entry and exit time in slots TRIMUL_TL_WAIT_BASE + 2 * slot (+ 1), slot < 3.
  * Replaces `_A2ADeviceSignal` and the `quiet` + `barrier_all` drains
  * (fold_cp_ops/distributed/workflows/trimul_autotuned.py:322-560, 3272-3300). */
 int trimul_sm100_peer_signal(void* const* flag_peers, int32_t cp, int32_t slot, trimul_stream_t stream);
 int trimul_sm100_peer_wait(const void* local_flags, int32_t slot, uint64_t expected, trimul_status_t* status,
-                           uint64_t timeout_ns, trimul_stream_t stream);
+                           uint64_t* timeline /* nullable */, uint64_t timeout_ns, trimul_stream_t stream);
 
 #ifdef __cplusplus
 }

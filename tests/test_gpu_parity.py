@@ -214,25 +214,26 @@ def test_kernel_tri_contract(N, planes_d):
 
 
 @pytest.mark.parametrize("N", [8, 200, 512])
-def test_kernel_tri_contract_pair_form_equals_single_cta_form(N, monkeypatch):
+def test_kernel_tri_contract_pair_form_equals_single_cta_form(N):
     """The default contraction kernel works on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); the
-    single-CTA 128 x 256 kernel stays selectable.  Same K order, same fp32 accumulation: bitwise equal."""
+    single-CTA 128 x 256 kernel is a tuning choice.  Same K order, same fp32 accumulation: bitwise equal."""
     from fold_cp_ops_b200 import kernels as K
 
     torch.manual_seed(7 + N)
     D = 128
     ab = (0.5 * torch.randn(2, D, 1, N, N, device=DEV)).to(torch.bfloat16)
     outs = []
-    for bits in ("0", "16384"):
-        monkeypatch.setenv("TRIMUL_DEBUG_SKIP", bits)
+    for form in ("pair", "single", "auto"):
         tri = torch.full((D, 1, N, N), float("nan"), dtype=torch.bfloat16, device=DEV)
         st = K.new_status(DEV)
-        K.tri_contract(K.make_geom(1, N, D, "outgoing", 1e-5), ab, [tri.data_ptr()], st)
+        K.tri_contract(K.make_geom(1, N, D, "outgoing", 1e-5), ab, [tri.data_ptr()], st, tuning=K.make_tuning(form))
         torch.cuda.synchronize()
         K.check_status(st)
         outs.append(tri)
     assert not torch.isnan(outs[0].float()).any()
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    with pytest.raises(ValueError, match="contract_form"):
+        K.make_tuning("triple")
 
 
 @pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0)])
@@ -336,11 +337,127 @@ def test_expired_wait_reports_status_and_context_survives():
     st = K.new_status(DEV)
     K.peer_wait(flags, 3, 1, st, timeout_ns=20_000_000)  # 20 ms; nobody signals slot 3
     torch.cuda.synchronize()
-    with pytest.raises(K.DeviceWaitTimeout, match="peer_sync"):
+    from fold_cp_ops_b200.distributed import CollectiveError
+
+    with pytest.raises(K.DeviceWaitTimeout, match="cross-rank flag wait expired") as info:
         K.check_status(st)
+    assert isinstance(info.value, CollectiveError)
     # the status was cleared and the context still works: a satisfied wait passes
     K.peer_signal([flags.data_ptr()], 3)
     K.peer_wait(flags, 3, 1, st, timeout_ns=20_000_000)
     torch.cuda.synchronize()
     K.check_status(st)
     assert int(flags[3].item()) == 1
+
+
+def test_engine_raises_on_the_next_forward_after_a_wait_gave_up():
+    """A forward whose status record shows an expired wait must not go unnoticed by a caller of the
+    public API: the next forward (and ``check``) raise ``DeviceWaitTimeout``."""
+    from fold_cp_ops_b200 import kernels as K
+
+    case = bf16_round_case(make_case(1, 32, 128, seed=21, bias="none", mask="none"))
+    eng = _engine(case)
+    x = case["x"].to(DEV).bfloat16()
+    eng.forward(x, "outgoing")
+    flags = torch.zeros(16, dtype=torch.int64, device=DEV)
+    K.peer_wait(flags, 1, 1, eng.status, timeout_ns=10_000_000)   # a wait nothing satisfies, on the engine's record
+    eng.forward(x, "outgoing")                                     # mirrors the record to the host
+    torch.cuda.synchronize()
+    with pytest.raises(K.DeviceWaitTimeout, match="BACK"):
+        eng.forward(x, "outgoing")
+    eng.forward(x, "outgoing")   # the record was cleared: the engine works again
+    torch.cuda.synchronize()
+    eng.check()
+
+
+# ------------------------------------------------------------------------------------------------
+# plans, tuning, statistics, the one-batch-plane path, the functional front door
+# ------------------------------------------------------------------------------------------------
+def test_plan_path_equals_stateless_entry_points():
+    """The engine launches through a plan (descriptors encoded once); the stateless per-kernel entry
+    points encode them per call.  Same kernels, same arguments: bitwise equal, also on the second use
+    of the plan with another output buffer."""
+    from fold_cp_ops_b200 import kernels as K
+
+    B, N, D = 2, 72, 128
+    case = bf16_round_case(make_case(B, N, D, seed=22, bias="all", mask="random"))
+    eng = _engine(case)
+    W = eng.weights
+    x = case["x"].to(DEV).bfloat16()
+    m = case["mask"].to(DEV)
+    for direction in ("outgoing", "incoming"):
+        ab = torch.empty((2, D, B, N, N), dtype=torch.bfloat16, device=DEV)
+        tri = torch.empty((D, B, N, N), dtype=torch.bfloat16, device=DEV)
+        gate = torch.empty((B, N, N, D), dtype=torch.bfloat16, device=DEV)
+        want = torch.empty_like(x)
+        K.forward_single(K.make_geom(B, N, D, direction, 1e-5), x, m, W.norm_in_w, W.norm_in_b, W.w_packed,
+                         W.bias_packed, W.w_fold, W.cd, ab, tri, gate, want, eng.status)
+        got1 = eng.forward(x, direction, m)
+        got2 = eng.forward(x, direction, m)
+        torch.cuda.synchronize()
+        eng.check()
+        assert torch.equal(got1, want) and torch.equal(got2, want)
+
+
+def test_one_batch_plane_at_a_time_equals_full_batch(monkeypatch):
+    """``CPO_TRIMUL_WORKSPACE_BYTES`` smaller than the full-batch workspace makes the cp=1 engine run one
+    batch plane per launch (what B=2, N=8192, D=128 needs on one GPU); batch planes are independent, so
+    the result is the same as the full-batch run and inside the oracle bound."""
+    case = bf16_round_case(make_case(2, 80, 128, seed=23, bias="all", mask="pad"))
+    ref = trimul_oracle(case["x"], "incoming", case["mask"], **weights_of(case))
+    full = _run(case, "incoming")
+    monkeypatch.setenv("CPO_TRIMUL_WORKSPACE_BYTES", "1")
+    eng = _engine(case)
+    out = eng.forward(case["x"].to(DEV).bfloat16(), "incoming", case["mask"].to(DEV))
+    torch.cuda.synchronize()
+    eng.check()
+    assert next(iter(eng._ws.values())).planes_b == 1
+    assert torch.equal(out.float().cpu(), full)
+    _assert_parity(out.float().cpu(), ref, "one batch plane per launch")
+
+
+def test_workspace_cache_is_fifo_and_results_survive_eviction(monkeypatch):
+    monkeypatch.setenv("CPO_TRIMUL_RECV_CACHE", "1")
+    case_a = bf16_round_case(make_case(1, 32, 128, seed=24, bias="none", mask="none"))
+    eng = _engine(case_a)
+    xa = case_a["x"].to(DEV).bfloat16()
+    xb = xa[:, :24, :24].contiguous()
+    a1 = eng.forward(xa, "outgoing")
+    assert list(eng._ws) == [(1, 32)]
+    eng.forward(xb, "outgoing")
+    assert list(eng._ws) == [(1, 24)]          # the older workspace was evicted
+    a2 = eng.forward(xa, "outgoing")
+    torch.cuda.synchronize()
+    eng.check()
+    assert list(eng._ws) == [(1, 32)] and torch.equal(a1, a2)
+
+
+def test_last_forward_stats_reports_kernel_times_and_spans():
+    case = bf16_round_case(make_case(1, 256, 128, seed=25, bias="none", mask="ones"))
+    eng = _engine(case)
+    x = case["x"].to(DEV).bfloat16()
+    eng.forward(x, "outgoing")
+    eng.collect_stats = True
+    eng.forward(x, "outgoing")
+    st = eng.last_forward_stats()
+    assert set(st["stage_ms"]) == {"ln_gated_proj", "tri_contract", "ln_out_proj"}
+    assert all(v > 0 for v in st["stage_ms"].values())
+    assert st["wait_ms"] == {}                          # cp = 1: no cross-rank waits
+    sp = st["span_ms"]
+    assert 0 < sp["ln_gated_proj"] <= sp["forward"] and 0 < sp["tri_contract"] and 0 < sp["ln_out_proj"]
+    assert 0 <= sp["first_store_after_start"] <= sp["ln_gated_proj"]
+    assert st["bytes_to_peers"] == {"front": 0, "back": 0}
+
+
+def test_trimul_a2a_functional_front_door_on_one_gpu():
+    """``trimul_a2a`` with a plain tensor (or a one-device mesh) routes to the single-GPU chain."""
+    from fold_cp_ops_b200.distributed.workflows.trimul_autotuned import trimul_a2a
+
+    case = bf16_round_case(make_case(1, 64, 128, seed=26, bias="all", mask="random"))
+    w = {k: (None if v is None else v.to(DEV)) for k, v in weights_of(case).items()}
+    for direction in ("outgoing", "incoming"):
+        ref = trimul_oracle(case["x"], direction, case["mask"], **weights_of(case))
+        got = trimul_a2a(case["x"].to(DEV).bfloat16(), w, torch.bfloat16, direction=direction, mask=case["mask"].to(DEV))
+        _assert_parity(got.float().cpu(), ref, f"trimul_a2a {direction}")
+    with pytest.raises(TypeError, match="unknown fused_kwargs"):
+        trimul_a2a(case["x"].to(DEV).bfloat16(), w, torch.bfloat16, back_cluster=2)

@@ -59,6 +59,28 @@ def test_static_scratch_forward_matches_regular_forward_twice(direction):
         assert torch.equal(out, want), (out.float() - want.float()).abs().max().item()
 
 
+def test_static_scratch_accepts_the_exact_capacity_shape():
+    """B=1, N=128, D=256 needs 8 * 128 * 128 * 256 bytes = exactly the 32 MiB the array holds."""
+    from fold_cp_ops_b200 import _lib
+
+    B, N, D = 1, 128, 256
+    assert 8 * B * N * N * D == _lib.STATIC_SCRATCH_BYTES
+    K, dev, case, W, x, m = _setup(B, N, D, seed=79)
+    geom = K.make_geom(B, N, D, "outgoing", 1e-5)
+    st = K.new_status(dev)
+    ab = torch.empty((2, D, B, N, N), dtype=torch.bfloat16, device=dev)
+    tri = torch.empty((D, B, N, N), dtype=torch.bfloat16, device=dev)
+    gate = torch.empty((B, N, N, D), dtype=torch.bfloat16, device=dev)
+    want = torch.empty_like(x)
+    K.forward_single(geom, x, m, W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed, W.w_fold, W.cd, ab, tri, gate,
+                     want, st)
+    got = torch.full_like(x, float("nan"))
+    K.forward_static(geom, x, m, W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed, W.w_fold, W.cd, got, st)
+    torch.cuda.synchronize()
+    K.check_status(st)
+    assert torch.equal(got, want)
+
+
 def test_static_scratch_refuses_shapes_beyond_its_capacity():
     from fold_cp_ops_b200 import _lib
 
