@@ -1,19 +1,22 @@
-"""Group-uniform decisions and bounded barriers.
+"""Decisions a whole process group takes together, and a barrier that cannot wait forever.
 
-Public surface of the reference's ``fold_cp_ops/distributed/collective_symmetry.py:113-365``:
-``CollectiveGate`` (``agree_bool``, ``barrier``, ``guard``, ``should_skip``) and the exception
-family ``CollectiveError`` > ``CollectiveFailure`` / ``PeerFailure`` / ``BarrierTimeout``.  The
-rule they enforce: a decision one rank could make differently from its peers (an exception, a
-skip, an out-of-memory) is reduced over the group BEFORE anyone acts on it, so ranks leave a
-collective region together or not at all.  Works on any backend (NCCL on GPUs, gloo on CPUs).
+Same public names as the reference's ``fold_cp_ops/distributed/collective_symmetry.py:113-365``
+(``CollectiveGate`` with ``agree_bool`` / ``barrier`` / ``guard`` / ``should_skip``, and the
+``CollectiveError`` family), written for this package.
+
+Why it exists: ranks of one job run the same program, but some outcomes are local -- an exception,
+a "this shape is not supported here", an out-of-memory.  A rank that acts on such an outcome alone
+(returns early, skips, raises) leaves its peers inside the next collective waiting for a partner
+that never comes.  The gate turns every such outcome into ONE small reduction first: afterwards all
+ranks know whether anybody tripped, and they leave the region together.  It needs nothing but
+``torch.distributed``, so it works over NCCL on GPUs and over gloo on CPUs alike.
 """
 from __future__ import annotations
 
-import contextlib
 import datetime
 import os
 import time
-from typing import Optional
+from typing import Callable, Dict, Optional
 
 import torch
 import torch.distributed as dist
@@ -22,43 +25,90 @@ __all__ = ["CollectiveGate", "CollectiveError", "CollectiveFailure", "PeerFailur
            "DEFAULT_BARRIER_TIMEOUT_S"]
 
 DEFAULT_BARRIER_TIMEOUT_S = float(os.environ.get("CPO_BARRIER_TIMEOUT_S", "480"))
-_POLL_S = 0.05
 
 
 class CollectiveError(RuntimeError):
-    """The group disagreed (base class)."""
+    """Root of the family: something about the group, not about this rank's own data, went wrong."""
 
 
 class CollectiveFailure(CollectiveError):
-    """This rank's own guarded block failed; chained to the original exception."""
+    """Raised on the rank whose guarded block threw; ``__cause__`` is that exception."""
 
 
 class PeerFailure(CollectiveError):
-    """This rank's guarded block succeeded but a peer's did not; the peer's log has the cause."""
+    """Raised on ranks whose guarded block was fine while a peer's threw."""
 
 
 class BarrierTimeout(CollectiveError):
-    """A bounded barrier did not complete within its bound."""
+    """A bounded barrier ran out of time: some peer never arrived."""
+
+
+# ---------------------------------------------------------------------------------------------
+# three ways to wait for an asynchronous barrier; each returns True when it completed in time
+# ---------------------------------------------------------------------------------------------
+def _wait_by_polling(work, bound_s: float) -> bool:
+    give_up_at = time.monotonic() + bound_s
+    while time.monotonic() <= give_up_at:
+        if work.is_completed():
+            return True
+        time.sleep(0.05)
+    return work.is_completed()
+
+
+def _wait_on_handle(work, bound_s: float) -> bool:
+    try:
+        return work.wait(timeout=datetime.timedelta(seconds=bound_s)) is not False
+    except Exception:  # noqa: BLE001 - backends signal an expired wait by raising
+        return False
+
+
+_ASYNC_WAITS: Dict[str, Callable[[object, float], bool]] = {"poll": _wait_by_polling, "wait": _wait_on_handle}
+
+
+class _GuardedRegion:
+    """Context manager behind :meth:`CollectiveGate.guard`.  Swallows the block's exception, asks the
+    group whether anybody has one, and re-raises in the matching form on every rank."""
+
+    def __init__(self, gate: "CollectiveGate", what: str):
+        self._gate, self._what = gate, what
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        anyone_failed = self._gate.agree_bool(exc is not None, op="any")
+        if not anyone_failed:
+            return False
+        me = self._gate.rank
+        if exc is None:
+            raise PeerFailure(
+                f"[{self._what}] succeeded on rank {me} but FAILED on at least one peer, so this rank stops here "
+                "rather than entering the next collective alone. The failing rank's log holds the original "
+                "traceback.")
+        raise CollectiveFailure(
+            f"[{self._what}] failed on rank {me} (surfaced collectively so no rank proceeds alone): "
+            f"{type(exc).__name__}: {exc}") from exc
 
 
 class CollectiveGate:
-    """One per process group.  Every method is COLLECTIVE: all ranks must reach it, in order."""
+    """Group-wide agreement for one process group.  Every method is COLLECTIVE -- all ranks of the
+    group call it, in the same order."""
 
     def __init__(self, group=None, device=None, timeout_s: float = DEFAULT_BARRIER_TIMEOUT_S):
-        if not (dist.is_available() and dist.is_initialized()):
+        if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError(
                 "CollectiveGate needs an initialized torch.distributed process group; call "
                 "init_process_group first. Constructing it earlier hides the real error behind a "
                 "collective failure several frames later.")
         self.group = group
         self.timeout_s = timeout_s
-        if device is None:
-            backend = dist.get_backend(group)
-            if "nccl" in str(backend) and torch.cuda.is_available():
-                device = torch.device("cuda", torch.cuda.current_device())
-            else:
-                device = torch.device("cpu")
-        self.device = torch.device(device)
+        self.device = torch.device(device) if device is not None else self._vote_device(group)
+
+    @staticmethod
+    def _vote_device(group) -> torch.device:
+        """Where the one-element vote tensor lives: the current GPU under NCCL, the host otherwise."""
+        on_gpu = "nccl" in str(dist.get_backend(group)) and torch.cuda.is_available()
+        return torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
 
     @property
     def rank(self) -> int:
@@ -68,69 +118,49 @@ class CollectiveGate:
     def world_size(self) -> int:
         return dist.get_world_size(self.group)
 
+    # -----------------------------------------------------------------------------------------
     def agree_bool(self, local: bool, *, op: str = "any") -> bool:
-        """``"any"``: true if any rank passed True; ``"all"``: only if every rank did."""
-        if op not in ("any", "all"):
+        """Reduce one boolean over the group: ``"any"`` is true when at least one rank said True,
+        ``"all"`` only when every rank did."""
+        reducers = {"any": dist.ReduceOp.MAX, "all": dist.ReduceOp.MIN}
+        if op not in reducers:
             raise ValueError(f"op must be 'any' or 'all'; got {op!r}")
-        t = torch.tensor([1.0 if local else 0.0], device=self.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "any" else dist.ReduceOp.MIN, group=self.group)
-        return bool(t.item() > 0)
+        vote = torch.full((1,), int(bool(local)), dtype=torch.int32, device=self.device)
+        dist.all_reduce(vote, op=reducers[op], group=self.group)
+        return int(vote.item()) == 1
 
     def barrier(self, timeout_s: Optional[float] = None) -> None:
-        """Barrier that raises :class:`BarrierTimeout` instead of waiting forever.
+        """A barrier with a bound: :class:`BarrierTimeout` instead of an endless wait.
 
-        ``CPO_BARRIER_WAIT`` selects how the wait is done: ``poll`` (default; poll the async work
-        handle), ``wait`` (``work.wait(timeout)``), ``sync`` (plain blocking barrier, unbounded)."""
-        bound = self.timeout_s if timeout_s is None else timeout_s
-        if bound <= 0:
-            raise ValueError(f"barrier timeout must be positive; got {bound}")
-        mode = os.environ.get("CPO_BARRIER_WAIT", "poll")
-        if mode == "sync":
-            if self.device.type == "cuda":
-                dist.barrier(group=self.group, device_ids=[self.device.index])
-            else:
-                dist.barrier(group=self.group)
+        ``CPO_BARRIER_WAIT`` picks the waiting style: ``poll`` (default) polls the asynchronous
+        handle, ``wait`` blocks on it with a timeout, ``sync`` is the plain blocking barrier (no
+        bound; for backends whose handles cannot be polled)."""
+        bound_s = self.timeout_s if timeout_s is None else timeout_s
+        if bound_s <= 0:
+            raise ValueError(f"barrier timeout must be positive; got {bound_s}")
+        style = os.environ.get("CPO_BARRIER_WAIT", "poll")
+        if style == "sync":
+            extra = {"device_ids": [self.device.index]} if self.device.type == "cuda" else {}
+            dist.barrier(group=self.group, **extra)
             return
-        work = dist.barrier(group=self.group, async_op=True)
-        if work is None:
+        handle = dist.barrier(group=self.group, async_op=True)
+        if handle is None:  # a one-rank group has nothing to wait for
             return
-        gone = (f"rank {self.rank} waited {bound:.0f}s at a collective barrier and at least one peer never "
+        if not _ASYNC_WAITS.get(style, _wait_by_polling)(handle, bound_s):
+            raise BarrierTimeout(
+                f"rank {self.rank} waited {bound_s:.0f}s at a collective barrier and at least one peer never "
                 "arrived. The group is now desynchronized -- do NOT enter another collective. A peer has died, "
                 "hung, or taken a divergent path (a per-rank skip or an unguarded exception are the usual causes).")
-        if mode == "wait":
-            try:
-                done = work.wait(timeout=datetime.timedelta(seconds=bound))
-            except Exception as exc:  # noqa: BLE001 - any failure here means the bound was not honoured
-                raise BarrierTimeout(gone) from exc
-            if done is False:
-                raise BarrierTimeout(gone)
-            return
-        deadline = time.monotonic() + bound
-        while not work.is_completed():
-            if time.monotonic() > deadline:
-                raise BarrierTimeout(gone)
-            time.sleep(_POLL_S)
 
-    @contextlib.contextmanager
-    def guard(self, what: str):
-        """A failure inside the block on ANY rank raises on EVERY rank, after one reduction."""
-        held: Optional[BaseException] = None
-        try:
-            yield
-        except BaseException as exc:  # noqa: BLE001 - re-raised after the reduction
-            held = exc
-        if not self.agree_bool(held is not None, op="any"):
-            return
-        if held is not None:
-            raise CollectiveFailure(
-                f"[{what}] failed on rank {self.rank} (surfaced collectively so no rank proceeds alone): "
-                f"{type(held).__name__}: {held}") from held
-        raise PeerFailure(
-            f"[{what}] succeeded on rank {self.rank} but FAILED on at least one peer, so this rank stops here "
-            "rather than entering the next collective alone. The failing rank's log holds the original traceback.")
+    def guard(self, what: str) -> _GuardedRegion:
+        """``with gate.guard("build"): ...`` -- if the block raises on ANY rank, EVERY rank raises after
+        one reduction: :class:`CollectiveFailure` (chained to the cause) where it happened,
+        :class:`PeerFailure` elsewhere.  A block that succeeds everywhere is left untouched."""
+        return _GuardedRegion(self, what)
 
     def should_skip(self, local_reason: Optional[str]) -> Optional[str]:
-        """Skip together or not at all: returns the agreed reason, or ``None`` to proceed."""
-        if not self.agree_bool(local_reason is not None, op="any"):
-            return None
-        return local_reason or "a peer rank requested a skip (this rank's own predicate passed)"
+        """All ranks skip or none does.  Returns ``None`` to carry on, otherwise the reason: this
+        rank's own if it had one, a note that a peer asked if it did not."""
+        if self.agree_bool(local_reason is not None, op="any"):
+            return local_reason or "a peer rank requested a skip (this rank's own predicate passed)"
+        return None

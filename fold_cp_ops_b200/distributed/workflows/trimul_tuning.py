@@ -1,94 +1,115 @@
-"""Typed tuning knobs for the fused TriMul, kept for call-site compatibility.
+"""Typed tuning surface of the fused TriMul.
 
-Same types and field names as the reference's
-``fold_cp_ops/distributed/workflows/trimul_tuning.py:72-217``: ``TriMulTuning`` nests
-``FrontTuning`` / ``BackTuning`` / ``OutGateTuning`` / ``TransportTuning``; every field defaults to
-``None`` and ``TriMulTuning().to_engine_kwargs() == {}``.  The reference's knobs select SM90 tile
-shapes, cluster widths and NVSHMEM drains; the sm_100a kernels have one fixed configuration per
-feature width, so the engine accepts the flattened keywords and ignores the SM90-only ones
-(listed in ``IGNORED_ON_SM100``).
+Keeps the vocabulary of the reference's ``fold_cp_ops/distributed/workflows/trimul_tuning.py:72-217``
+-- ``TriMulTuning`` holding a ``FrontTuning``, ``BackTuning``, ``OutGateTuning`` and
+``TransportTuning``, every knob ``None`` until set, ``TriMulTuning().to_engine_kwargs() == {}`` -- so
+call sites written against it keep working, and adds the choices the sm_100a kernels really have:
+
+    BackTuning.contract_form        "auto" | "single" | "pair": one CTA per 128 x 256 tile of the
+                                    contraction, or a CTA pair (tcgen05 cta_group::2) per 256 x 256 tile
+    FrontTuning.fixed_order         True: every CTA of the projection kernel walks its gated chunks in
+                                    the same order (default: rotated, which spreads the peer stores)
+    TransportTuning.wait_timeout_ms bound of the cross-rank flag waits
+
+The reference's remaining knobs pick SM90 tile shapes, cluster widths and NVSHMEM drains.  They are
+still accepted and reach the engine under the engine's own spelling, where they change nothing
+(``IGNORED_ON_SM100``).  ``engine.SM100_DEFAULTS`` holds the measured default per (feature width, cp).
+
+How a knob is declared: ``_knob("engine_keyword")`` is a dataclass field defaulting to ``None`` whose
+metadata carries the engine's keyword; ``_tuning_group`` freezes the class and derives its
+``_ENGINE_KEYS`` table from that metadata, so a field and its keyword cannot drift apart.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, fields
-from typing import Any, Dict, Optional, Tuple
+import dataclasses
+from typing import Any, Dict, Iterator, Optional, Tuple
 
 __all__ = ["TriMulTuning", "FrontTuning", "BackTuning", "OutGateTuning", "TransportTuning", "NOT_EXPOSED",
            "IGNORED_ON_SM100"]
 
 
-@dataclass(frozen=True)
+def _knob(engine_keyword: str):
+    return dataclasses.field(default=None, metadata={"engine_keyword": engine_keyword})
+
+
+def _tuning_group(cls):
+    """Freeze ``cls`` as a dataclass and publish ``cls._ENGINE_KEYS`` = {field name: engine keyword}."""
+    cls = dataclasses.dataclass(frozen=True)(cls)
+    cls._ENGINE_KEYS = {f.name: f.metadata["engine_keyword"] for f in dataclasses.fields(cls)
+                        if "engine_keyword" in f.metadata}
+    return cls
+
+
+def _set_knobs(group) -> Iterator[Tuple[str, Any]]:
+    """(engine keyword, value) of every knob of ``group`` that is not ``None``."""
+    for name, keyword in type(group)._ENGINE_KEYS.items():
+        value = getattr(group, name)
+        if value is not None:
+            yield keyword, value
+
+
+@_tuning_group
 class FrontTuning:
-    """Stage 2 (gated projection + front reshard)."""
-    tile_mn: Optional[Tuple[int, int]] = None
-    pad_inner: Optional[bool] = None
-    pad_eager: Optional[bool] = None
-    _ENGINE_KEYS = {"tile_mn": "front_tile_mn", "pad_inner": "front_pad_inner", "pad_eager": "front_pad_eager"}
+    """The gated projection kernel and the front reshard it carries."""
+    tile_mn: Optional[Tuple[int, int]] = _knob("front_tile_mn")
+    pad_inner: Optional[bool] = _knob("front_pad_inner")
+    pad_eager: Optional[bool] = _knob("front_pad_eager")
+    fixed_order: Optional[bool] = _knob("front_fixed_order")
 
 
-@dataclass(frozen=True)
+@_tuning_group
 class BackTuning:
-    """Stage 3 (triangle contraction + back reshard)."""
-    tile_mn: Optional[Tuple[int, int]] = None
-    pingpong: Optional[bool] = None
-    cluster_n: Optional[int] = None
-    _ENGINE_KEYS = {"tile_mn": "back_tile_mn", "pingpong": "back_pingpong", "cluster_n": "back_cluster_n"}
+    """The triangle contraction kernel and the back reshard it carries."""
+    tile_mn: Optional[Tuple[int, int]] = _knob("back_tile_mn")
+    pingpong: Optional[bool] = _knob("back_pingpong")
+    cluster_n: Optional[int] = _knob("back_cluster_n")
+    contract_form: Optional[str] = _knob("contract_form")
 
 
-@dataclass(frozen=True)
+@_tuning_group
 class OutGateTuning:
-    """Stage 4 (output LayerNorm + gated output projection)."""
-    consumer: Optional[str] = None
-    _ENGINE_KEYS = {"consumer": "consumer"}
+    """The output LayerNorm + gated output projection."""
+    consumer: Optional[str] = _knob("consumer")
 
 
-@dataclass(frozen=True)
+@_tuning_group
 class TransportTuning:
-    """Completion signalling of the two reshards."""
-    device_signal_nvlink: Optional[bool] = None
-    _ENGINE_KEYS = {"device_signal_nvlink": "use_device_signal_nvlink"}
+    """How ranks learn that a reshard has landed."""
+    device_signal_nvlink: Optional[bool] = _knob("use_device_signal_nvlink")
+    wait_timeout_ms: Optional[float] = _knob("wait_timeout_ms")
 
 
-@dataclass(frozen=True)
+@_tuning_group
 class TriMulTuning:
-    """The whole surface; inert by default."""
-    front: FrontTuning = field(default_factory=FrontTuning)
-    back: BackTuning = field(default_factory=BackTuning)
-    out_gate: OutGateTuning = field(default_factory=OutGateTuning)
-    transport: TransportTuning = field(default_factory=TransportTuning)
-    autotune: Optional[bool] = None
-    persistent: Optional[bool] = None
-    _ENGINE_KEYS = {"autotune": "autotune_config", "persistent": "is_persistent"}
+    """Everything tunable about one fused TriMul module; changes nothing until a knob is set."""
+    front: FrontTuning = dataclasses.field(default_factory=FrontTuning)
+    back: BackTuning = dataclasses.field(default_factory=BackTuning)
+    out_gate: OutGateTuning = dataclasses.field(default_factory=OutGateTuning)
+    transport: TransportTuning = dataclasses.field(default_factory=TransportTuning)
+    autotune: Optional[bool] = _knob("autotune_config")
+    persistent: Optional[bool] = _knob("is_persistent")
 
     def to_engine_kwargs(self) -> Dict[str, Any]:
-        """Flatten to engine keyword names, omitting every unset field (``{}`` when nothing is set)."""
-        out: Dict[str, Any] = {}
-        for group in (self.front, self.back, self.out_gate, self.transport):
-            for f in fields(group):
-                v = getattr(group, f.name)
-                if v is not None:
-                    out[type(group)._ENGINE_KEYS[f.name]] = v
-        for name, key in TriMulTuning._ENGINE_KEYS.items():
-            v = getattr(self, name)
-            if v is not None:
-                out[key] = v
-        return out
+        """The set knobs as engine constructor keywords; an untouched tuning gives ``{}``."""
+        flat: Dict[str, Any] = {}
+        for group in (self.front, self.back, self.out_gate, self.transport, self):
+            flat.update(_set_knobs(group))
+        return flat
 
 
-#: engine keywords that exist for call-site compatibility and change nothing on sm_100a
+#: engine keywords kept for call sites written against the SM90 engine; the sm_100a kernels have no
+#: such choice and ignore them
 IGNORED_ON_SM100 = ("front_tile_mn", "front_pad_inner", "front_pad_eager", "back_tile_mn", "back_pingpong",
                     "back_cluster_n", "consumer", "use_device_signal_nvlink", "autotune_config", "is_persistent")
 
-#: engine parameters deliberately not reachable through the tuning surface, with the reason
+#: engine constructor keywords that are deliberately NOT tuning knobs, each with the reason
 NOT_EXPOSED = {
-    "back_store": "one store design exists: the contraction epilogue writes to the token owner",
-    "hybrid_ib": "single NVSwitch domain only; there is no InfiniBand transport",
-    "route2_ni": "derived from (direction, cp1) -- a receive layout, not a speed",
-    "composite_k": "derived from (direction, cp1) -- a receive layout, not a speed",
-    "dynamic": "one supported value",
-    "has_mask": "a property of the call, not a tuning choice",
-    "eps": "a model hyperparameter, promoted to a named constructor argument",
-    "front_pingpong": "the projection kernel has one schedule",
-    "device_mesh": "topology, taken from the constructor",
-    "placements": "topology, taken from the constructor",
+    "device_mesh": "where the ranks are: the module's constructor argument, not a speed",
+    "placements": "how the tensor is sharded: the module's constructor argument, not a speed",
+    "dynamic": "only True exists: one engine serves every token extent",
+    "has_mask": "decided by whether the call passes a mask",
+    "eps": "a hyperparameter of the model, passed by name to the module",
+    "composite_k": "names the incoming receive layout on a 1-D shard; follows from (direction, cp1)",
+    "route2_ni": "names the incoming receive layout on a 2-D shard; follows from (direction, cp1)",
+    "allocate": "whether the constructor allocates its buffers at once; a lifetime choice, not a speed",
 }

@@ -15,12 +15,17 @@ from torch import Tensor
 
 from ..engine import TriMulEngine
 
-__all__ = ["trimul_autotuned", "TRIMUL_VARIANTS"]
+__all__ = ["trimul_autotuned", "TRIMUL_VARIANTS", "clear_cache"]
 
 #: the kernel chains this build can run (the reference lists five SM90 combos here)
 TRIMUL_VARIANTS = ("sm100_fused",)
 
-_ENGINE_CACHE: "OrderedDict[tuple, TriMulEngine]" = OrderedDict()
+#: engines (packed weights + workspaces) keyed on the identity of the twelve weight tensors.  An entry
+#: keeps references to those tensors, so their storage cannot be freed and handed to another model of the
+#: same shapes while the entry lives.  The key includes each tensor's version counter: in-place updates
+#: through autograd-visible ops (``copy_``, ``add_`` ...) repack the weights; writes that bypass the
+#: counter (``param.data.copy_(...)``) do NOT -- call :func:`clear_cache` after loading weights that way.
+_ENGINE_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
 _ENGINE_CACHE_CAP = 8
 
 
@@ -32,15 +37,28 @@ def _weight_key(t: Optional[Tensor]):
 
 def _engine_for(device, eps, w: dict) -> TriMulEngine:
     key = (str(device), float(eps)) + tuple(_weight_key(w[k]) for k in sorted(w))
-    eng = _ENGINE_CACHE.get(key)
-    if eng is None:
-        eng = TriMulEngine(w, device=device, eps=eps)
-        _ENGINE_CACHE[key] = eng
+    entry = _ENGINE_CACHE.get(key)
+    if entry is None:
+        entry = (TriMulEngine(w, device=device, eps=eps), tuple(w[k] for k in sorted(w)))
+        _ENGINE_CACHE[key] = entry
         while len(_ENGINE_CACHE) > _ENGINE_CACHE_CAP:
-            _ENGINE_CACHE.popitem(last=False)
+            _ENGINE_CACHE.popitem(last=False)[1][0].free()
     else:
         _ENGINE_CACHE.move_to_end(key)
-    return eng
+    return entry[0]
+
+
+def clear_cache() -> None:
+    """Drop every cached single-GPU engine (packed weights, workspaces).  Needed after weights were
+    overwritten in a way their version counters do not see."""
+    while _ENGINE_CACHE:
+        _ENGINE_CACHE.popitem()[1][0].free()
+
+
+def engines_for_weights(w: dict):
+    """The cached engines that were built from exactly these weight tensors (by identity)."""
+    mine = {id(t) for t in w.values() if t is not None}
+    return [eng for eng, kept in _ENGINE_CACHE.values() if {id(t) for t in kept if t is not None} <= mine and mine]
 
 
 def trimul_autotuned(

@@ -94,6 +94,29 @@ def trimul_stages(x, direction, mask, norm_in_w, norm_in_b, p_in_w, g_in_w, norm
     return {"xn": xn, "a": a, "b": b, "tri": tri, "trin": trin, "gate": gate, "out": out}
 
 
+def trimul_eager_module(x, direction, mask=None, *, eps=1e-5, **w) -> torch.Tensor:
+    """The same forward in the spelling of the reference's eager ``nn.Module``
+    (``benchmark/distributed/trimul_dtensor_reference.py:1841-1847``: ``nn.LayerNorm`` / ``nn.Linear``
+    submodules, the mask applied before the chunk, one ``einsum`` at fp32, the output gate on ``xn``),
+    written with the functional forms of those modules.  Equal to :func:`trimul_oracle` up to fp32
+    summation order; on a CPU it is the faster of the two spellings (fused LayerNorm, biases folded into
+    the GEMMs), which is why the timed CPU baseline reports both."""
+    import torch.nn.functional as F
+
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"direction must be 'outgoing' or 'incoming'; got {direction!r}")
+    D = x.shape[-1]
+    x = x.float()
+    xn = F.layer_norm(x, (D,), _f(w["norm_in_w"]), _f(w.get("norm_in_b")), eps)
+    ab = F.linear(xn, _f(w["p_in_w"]), _f(w.get("p_in_b"))) * torch.sigmoid(F.linear(xn, _f(w["g_in_w"]), _f(w.get("g_in_b"))))
+    if mask is not None:
+        ab = ab * mask.float().unsqueeze(-1)
+    a, b = torch.chunk(ab, 2, dim=-1)
+    tri = torch.einsum("bikd,bjkd->bijd" if direction == "outgoing" else "bkid,bkjd->bijd", a, b)
+    trin = F.layer_norm(tri, (D,), _f(w["norm_out_w"]), _f(w.get("norm_out_b")), eps)
+    return F.linear(trin, _f(w["p_out_w"]), _f(w.get("p_out_b"))) * torch.sigmoid(F.linear(xn, _f(w["g_out_w"]), _f(w.get("g_out_b"))))
+
+
 def trimul_oracle(x, direction, mask=None, *, eps=1e-5, **w) -> torch.Tensor:
     """``(B, N, N, D)`` fp32 TriMul forward; keyword weights as in the reference's 12-key dict."""
     return trimul_stages(x, direction, mask, eps=eps, **w)["out"]

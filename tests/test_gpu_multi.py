@@ -94,9 +94,27 @@ def _cp_parity(rank, world):
                                        run_check=False)
                 for rep in range(3):  # repeated forwards exercise the counters and the WAR guards
                     out = tm(x, m)
+                tm.check()  # synchronises; raises DeviceWaitTimeout if any bounded wait expired
+                # measured forward: kernel windows, cross-rank wait times and bytes pushed to peers
+                tm.collect_stats(True)
+                out_stats = tm(x, m)
+                st = tm.last_forward_stats()
+                tm.collect_stats(False)
+                assert torch.equal(out_stats.to_local(), out.to_local())
+                assert set(st["wait_ms"]) == {"front", "back", "consumed"} and all(v is not None and v >= 0 for v in st["wait_ms"].values())
+                assert all(v > 0 for v in st["stage_ms"].values())
+                s_bytes = B * (N // cp0) * (N // cp1) * D * 2
+                assert st["bytes_to_peers"] == {"front": 2 * s_bytes * (world - 1) // world, "back": s_bytes * (world - 1) // world}
+                # the functional front door builds its own engine (own symmetric buffers) and must agree bit for bit
+                from fold_cp_ops_b200.distributed.workflows.trimul_autotuned import trimul_a2a
+                cache = {}
+                w_dev = {k: (None if v is None else v.to(dm.device)) for k, v in weights_of(case).items()}
+                out_fn = trimul_a2a(x, w_dev, torch.bfloat16, direction=direction, mask=m, distributed_manager=dm, _cache=cache)
                 torch.cuda.synchronize()
-                for eng in tm._engines.values():
+                assert out_fn.placements == x.placements and torch.equal(out_fn.to_local(), out.to_local())
+                for eng in cache.values():
                     eng.check()
+                    eng.free()
                 assert out.shape == x.shape and out.placements == x.placements
                 got = out.to_local().float().cpu()
                 want = ref[sl]

@@ -186,7 +186,22 @@ def test_tuning_surface():
     legal = {n for n, p in inspect.signature(front.TriMulAutotuned.__init__).parameters.items()
              if p.kind is inspect.Parameter.KEYWORD_ONLY}
     assert set(t.to_engine_kwargs()) <= legal
-    assert "hybrid_ib" in NOT_EXPOSED
+    # the engine's keyword-only surface is partitioned: every knob is either reachable through the tuning
+    # types or listed in NOT_EXPOSED with a reason (the reference's own test of this module checks the same)
+    from fold_cp_ops_b200.distributed.workflows.trimul_tuning import OutGateTuning, TransportTuning
+    exposed = set(TriMulTuning._ENGINE_KEYS.values())
+    for group in (FrontTuning, BackTuning, OutGateTuning, TransportTuning):
+        exposed |= set(group._ENGINE_KEYS.values())
+        assert all(getattr(group(), f) is None for f in group.__dataclass_fields__)
+    assert exposed | set(NOT_EXPOSED) == legal and not (exposed & set(NOT_EXPOSED))
+    # the sm_100a knobs are real: they reach the engine under its own spelling
+    real = TriMulTuning(back=BackTuning(contract_form="single"), front=FrontTuning(fixed_order=True),
+                        transport=TransportTuning(wait_timeout_ms=500.0))
+    assert real.to_engine_kwargs() == {"front_fixed_order": True, "contract_form": "single", "wait_timeout_ms": 500.0}
+    with pytest.raises(TypeError, match="tile_mm"):
+        FrontTuning(tile_mm=(128, 128))
+    with pytest.raises(Exception):
+        FrontTuning().tile_mn = (1, 2)
 
 
 def test_incoming_store_variant_is_total():

@@ -123,3 +123,17 @@ def test_bounds_shapes():
     ref = torch.randn(4, 4)
     assert tolerance_bound(ref).shape == ref.shape
     assert cp1_bound(ref).shape == ref.shape
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_eager_module_spelling_equals_the_restatement(direction):
+    """The timed CPU baseline may use the eager-module spelling (fused LayerNorm, biases inside the
+    GEMMs): it must be the same function as the op-for-op restatement, up to fp32 summation order."""
+    from oracle.trimul_oracle import make_case, trimul_eager_module, trimul_oracle, weights_of
+
+    case = make_case(2, 40, 128, seed=31, bias="all", mask="pad")
+    a = trimul_oracle(case["x"], direction, case["mask"], **weights_of(case))
+    b = trimul_eager_module(case["x"], direction, case["mask"], **weights_of(case))
+    assert (a - b).abs().max().item() <= 2e-4 * max(1.0, a.abs().max().item())
+    nomask = trimul_eager_module(case["x"], direction, None, **weights_of(case))
+    assert torch.allclose(nomask, trimul_oracle(case["x"], direction, None, **weights_of(case)), atol=2e-4, rtol=1e-4)
