@@ -560,7 +560,7 @@ def run_ours(args):
                                           "on the device (%globaltimer at wait entry and exit): reshard time that was "
                                           "not hidden behind a kernel, rank skew included"}
         cpu = None
-        if not args.kernels_only:
+        if not args.kernels_only and cp == 1:  # the CPU baseline is reported on rank 0 of the one-GPU run only
             cores = os.cpu_count() or 1
             both = cpu_reference_time(D, direction, cores)
             name = max(both, key=lambda k: both[k][1])

@@ -14,6 +14,14 @@ if str(REPO) not in sys.path:
     sys.path.insert(0, str(REPO))
 
 
+def reference_root():
+    """A checkout of the reference project, if one is around: ``REFERENCE_ROOT``, else a directory named
+    ``reference`` beside this repository.  ``None`` when there is none (the GPU box has none)."""
+    env = os.environ.get("REFERENCE_ROOT")
+    cand = Path(env) if env else REPO.parent / "reference"
+    return cand if (cand / "fold_cp_ops" / "workflows" / "trimul_autotune.py").exists() else None
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device of compute capability 10.x (B200)")
 

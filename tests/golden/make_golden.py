@@ -50,7 +50,9 @@ def input_digest(case) -> str:
 
 
 def main() -> None:
-    ref_root = os.environ.get("REFERENCE_ROOT", "/root/reference")
+    ref_root = os.environ.get("REFERENCE_ROOT")
+    if not ref_root:
+        raise SystemExit("set REFERENCE_ROOT to a checkout of the reference project (the golden vectors are its outputs)")
     sys.path.insert(0, ref_root)
     sys.dont_write_bytecode = True
     from fold_cp_ops.workflows.trimul_autotune import trimul_ref  # type: ignore

@@ -204,6 +204,39 @@ def test_collective_gate_paths_on_two_cpu_ranks():
     assert res[0] == "timeout" and res[1] == "late"
 
 
+def _oom_vote(rank, world):
+    """Rank 1 pretends to have no free device memory: BOTH ranks must refuse the symmetric allocation with
+    ``torch.cuda.OutOfMemoryError`` (so neither enters the collective allocation alone); when both have
+    room, nobody raises."""
+    import torch.distributed as dist
+
+    from fold_cp_ops_b200.distributed import symmetric
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cpu = torch.device("cpu")
+    real = torch.cuda.mem_get_info
+    outcomes = []
+    try:
+        for free_by_rank in ({0: 64 << 30, 1: 1 << 20}, {0: 64 << 30, 1: 64 << 30}):
+            torch.cuda.mem_get_info = lambda device=None, _f=free_by_rank[rank]: (_f, 180 << 30)
+            try:
+                symmetric.refuse_unsatisfiable_request(8 << 30, cpu, dist.group.WORLD)
+                outcomes.append("fits")
+            except torch.cuda.OutOfMemoryError as exc:
+                assert "refused on every rank" in str(exc)
+                outcomes.append("refused")
+    finally:
+        torch.cuda.mem_get_info = real
+    dist.barrier()
+    dist.destroy_process_group()
+    return outcomes
+
+
+def test_symmetric_oom_is_refused_on_every_rank_together():
+    res = _run("_oom_vote")
+    assert res[0] == ["refused", "fits"] and res[1] == ["refused", "fits"]
+
+
 # ------------------------------------------------------------------------------------------------
 # launcher detection (single process, monkeypatched environment)
 # ------------------------------------------------------------------------------------------------

@@ -12,7 +12,9 @@ from oracle.trimul_oracle import (bf16_round_case, cp1_bound, make_case, toleran
                                   trimul_stages, weights_of)
 from tests.golden.make_golden import CASES, input_digest
 
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+from tests.conftest import reference_root
+
+REFERENCE_ROOT = str(reference_root() or "")
 
 
 def _case(name):
