@@ -419,7 +419,7 @@ def run_ours(args):
     wait_ms = {}
     engines = trimul._live_engines()
     eng = engines[-1] if engines else None
-    if eng is not None and not args.kernels_only:
+    if eng is not None and (args.stage_times or not args.kernels_only):
         # kernel-only CUDA-event windows (the flag kernels are outside them) and, at cp > 1, the time each
         # rank's stream sat in the three cross-rank flag waits (from %globaltimer stamps in the wait kernels)
         trimul.collect_stats(True)
@@ -683,6 +683,9 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input forward only (skip the e2e, CPU-baseline and verify legs); for profilers")
     ap.add_argument("--no-e2e", action="store_true", help="skip the pinned-host end-to-end leg")
+    ap.add_argument("--stage-times", action="store_true",
+                    help="with --kernels-only: still report the per-kernel times (used with profiling builds of the "
+                         "library selected by CPO_TRIMUL_LIB, whose results are wrong by construction)")
     ap.add_argument("--verify", action="store_true", default=True)
     ap.add_argument("--no-verify", dest="verify", action="store_false")
     args = ap.parse_args()

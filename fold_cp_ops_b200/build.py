@@ -45,10 +45,16 @@ def is_stale() -> bool:
     return any(d.exists() and d.stat().st_mtime > t for d in deps)
 
 
-def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every kernel for sm_100a into one shared library; returns its path."""
+def build(verbose: bool = False, ptxas_info: bool = False, ablate: int = 0) -> Path:
+    """Compile every kernel for sm_100a into one shared library; returns its path.
+
+    ``ablate`` != 0 builds a PROFILING library ``libtrimul_sm100_ablate<bits>.so`` beside the real one, in
+    which roles of the projection kernel do no work (``TRIMUL_ABLATE`` in ``csrc/ln_gated_proj.cu``); select
+    it with ``CPO_TRIMUL_LIB``.  Its results are wrong by construction; it only exists to be timed."""
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if ptxas_info else []), "-o", str(LIB_PATH), *srcs]
+    out = LIB_PATH if not ablate else PKG_DIR / f"libtrimul_sm100_ablate{int(ablate)}.so"
+    extra = [f"-DTRIMUL_ABLATE={int(ablate)}"] if ablate else []
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if ptxas_info else []), "-o", str(out), *srcs]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -56,7 +62,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
     if verbose or ptxas_info:
         sys.stderr.write(proc.stderr)
-    return LIB_PATH
+    return out
 
 
 def ensure_built() -> Path:
@@ -66,5 +72,5 @@ def ensure_built() -> Path:
 
 
 if __name__ == "__main__":
-    build(verbose=True, ptxas_info="--ptxas" in sys.argv)
-    print(LIB_PATH)
+    bits = int(sys.argv[sys.argv.index("--ablate") + 1]) if "--ablate" in sys.argv else 0
+    print(build(verbose=True, ptxas_info="--ptxas" in sys.argv, ablate=bits))

@@ -33,6 +33,16 @@ namespace trimul {
 
 namespace {
 
+// Role ablation for profiling builds only: -DTRIMUL_ABLATE=<bits> compiles a SEPARATE library in which a role
+// of the projection kernel does no work (results are then wrong), so that the time each role adds can be
+// measured.  bit 0: epilogue math and staging, 1: LayerNorm loads / math / tile write, 2: MMA issue,
+// 3: a|b and gate stores, 4: weight loads after the first ring fill.  0 (the shipped library): every
+// `if (kAblate & x)` below is dead code.
+#ifndef TRIMUL_ABLATE
+#define TRIMUL_ABLATE 0
+#endif
+constexpr int kAblate = TRIMUL_ABLATE;
+
 constexpr int BM = 128;
 // Seven warpgroups: w0-3 control (w0 weight TMA, w1 MMA issue, w2 TMEM alloc), w4-19 epilogue,
 // w20-27 LayerNorm.  Launched at 72 registers per thread and rebalanced with setmaxnreg:
@@ -265,6 +275,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sm100::tma_prefetch_desc(&tmW);
       PipeState ps{0, 0};
       bool ok = true;
+      [[maybe_unused]] int n_loads = 0;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int ci = 0; ci < C::kNumChunks && ok; ++ci) {
           const int c = chunk_at<C::kGated>(ci, rot);
@@ -273,6 +284,11 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               report_timeout(p.status, kKernelGatedProj, 0, c * 16 + kb);
               ok = false;
               break;
+            }
+            if ((kAblate & 16) && n_loads++ >= C::kWStages) {
+              sm100::mbar_arrive(&ctl->w_full[ps.stage]);  // stale stage: no weight traffic
+              ps.advance(C::kWStages);
+              continue;
             }
             // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunk the last D rows
             const int rows = c < C::kGated ? C::kChunkN : D;
@@ -321,7 +337,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const uint64_t db = sm100::umma_desc_kmajor_sw128(sm100::smem_u32(w_tiles + ps.stage * C::kWStageBytes));
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
-              sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+              if (!(kAblate & 4)) sm100::umma_bf16_ss(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
             }
             sm100::umma_commit(&ctl->w_empty[ps.stage]);
             ps.advance(C::kWStages);
@@ -374,7 +390,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 stamped = true;
               }
 #pragma unroll 1
-              for (int k = 0; k < C::CH / 16; ++k) {
+              for (int k = 0; k < ((kAblate & 8) ? 0 : C::CH / 16); ++k) {
                 const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
                 const CUtensorMap* map = &om.ab[d >> p.d_loc_log2];
                 const int plane = h * d_loc_n + (d & d_loc_mask);
@@ -386,7 +402,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;
               const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
 #pragma unroll 1
-              for (int j = 0; j < C::kBoxesPerBuf; ++j) {
+              for (int j = 0; j < ((kAblate & 8) ? 0 : C::kBoxesPerBuf); ++j) {
                 const int jb = u * C::kBoxesPerBuf + j;  // gate box: channels [64 jb, 64 jb + 64)
                 sm100::tma_store_4d(&om.gate, src + j * C::kGateBoxBytes, jb * 64, cw, cl, tc.b);
               }
@@ -427,7 +443,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       for (int ps = 0; ps < PASSES; ++ps) {
         const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
         const int w = tc.w0 + r;
-        if (w < p.n_walk) {
+        if (w < p.n_walk && !(kAblate & 2)) {
           raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
         } else {
           raw[ps] = make_uint4(0, 0, 0, 0);
@@ -435,7 +451,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       // normalise in registers while the tensor core still reads the previous tile
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
+      for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
         float v[8];
         v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
         v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
@@ -467,7 +483,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       uint8_t* a_tile = a_tiles + buf * C::kABytes;
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
+      for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
         const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
         // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
         const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
@@ -535,7 +551,9 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
         sm100::tcgen05_fence_after_sync();
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kChunkN;
-        if (c < C::kGated) {
+        if (kAblate & 1) {
+          // ablated: no TMEM reads, no math, nothing staged
+        } else if (c < C::kGated) {
           // gated chunk: columns [0, CH) projection, [CH, 2CH) gate, same channel order
           constexpr int CW = C::CH / 4;   // channels of the chunk this warp handles
           constexpr int NS = CW / 16;     // in 16-channel sub-groups
