@@ -47,6 +47,7 @@ WORKLOADS = {
     # small cases for ncu captures (inputs > L2, < 2 GB on the device)
     "profile_n1024_d256": dict(B=1, N=1024, D=256, direction="outgoing", mesh="1d", mask="ones"),
     "profile_n2048_d128": dict(B=1, N=2048, D=128, direction="outgoing", mesh="1d", mask="ones"),
+    "profile_n2048_d256": dict(B=1, N=2048, D=256, direction="outgoing", mesh="1d", mask="ones"),
 }
 CPU_SAMPLE_N = 768  # token extent of the bounded CPU sample (same D, same distributions)
 E2E_MAX_BYTES = 24 << 30  # per-rank input size beyond which the pinned-host end-to-end leg is skipped

@@ -83,8 +83,8 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 }
 
 // try_wait with a suspend-time hint: the hardware may park the thread until the phase completes or
-// about `hint_ns` elapse, so a waiting warp does not burn issue slots its SM sub-partition shares
-// with the warps doing the work.
+// about `hint_ns` elapse.  Measured in all three kernels with hints of 1, 10 and 100 us against the
+// default time limit: no difference in kernel time, so mbar_wait uses the plain form.
 __device__ __forceinline__ bool mbar_test_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(

@@ -33,3 +33,27 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
 
 def test_reference_arm_is_silent_on_other_ranks():
     assert _run({"RANK": "1", "WORLD_SIZE": "2"}) == []
+
+
+def test_spot_check_patch_oracle_agrees_with_the_full_oracle():
+    """bench.py's full-size parity check evaluates the oracle on a patch only (rows / columns of the input
+    it needs).  On a small case its patch must agree with the full CPU oracle, for both directions and with
+    the padding mask, and it must notice a wrong output element."""
+    import torch
+
+    import bench
+    from oracle.trimul_oracle import trimul_oracle
+
+    wl = dict(B=2, N=160, D=128, mask="pad")
+    dev = torch.device("cpu")
+    w = bench.make_layer_weights(wl["D"], 0, dev)
+    x = torch.randn(wl["B"], wl["N"], wl["N"], wl["D"], generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    tm = bench.token_mask(wl["mask"], wl["N"])
+    mask = (tm[:, None] * tm[None, :]).expand(wl["B"], -1, -1)
+    for direction in ("outgoing", "incoming"):
+        full = trimul_oracle(x.float(), direction, mask, **{k: (None if v is None else v.float()) for k, v in w.items()})
+        res = bench.spot_check(w, x, full, wl, direction, 1, 1, 1, 0, 0, 0, dev, rows=2, cols=16)
+        assert res["within_bound_on_every_rank"] and res["max_abs_err"] < 1e-3, res
+        wrong = full.clone()
+        wrong[wl["B"] - 1] += 1.0
+        assert not bench.spot_check(w, x, wrong, wl, direction, 1, 1, 1, 0, 0, 0, dev, rows=2, cols=16)["within_bound_on_every_rank"]
