@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "trimul_sm100_workspace",
     "trimul_sm100_reshard_plan",
     "trimul_sm100_last_error",
+    "trimul_sm100_build_id",
     "trimul_sm100_pack_weights",
     "trimul_sm100_pack_out_weights",
     "trimul_sm100_ln_gated_proj",
@@ -104,16 +105,17 @@ def library_path() -> Path:
     return Path(override) if override else _PKG_DIR / LIB_NAME
 
 
-def override_is_default() -> bool:
-    return not os.environ.get("CPO_TRIMUL_LIB")
+def _stale_reason(lib) -> str:
+    """'' when the library was compiled from the sources beside it (or there are none to compare with)."""
+    if os.environ.get("CPO_TRIMUL_LIB") or not (_PKG_DIR / "csrc").is_dir():
+        return ""
+    lib.trimul_sm100_build_id.restype = C.c_char_p
+    lib.trimul_sm100_build_id.argtypes = []
+    built_from = lib.trimul_sm100_build_id().decode()
+    from .build import source_digest
 
-
-def _sources_newer_than(path: Path) -> bool:
-    """True when a kernel source or the public header was modified after the library was built."""
-    t = path.stat().st_mtime
-    deps = list((_PKG_DIR / "csrc").glob("*.cu*")) + list((_PKG_DIR / "csrc").glob("*.h")) + \
-        [_PKG_DIR.parent / "include" / "trimul_sm100.h"]
-    return any(d.exists() and d.stat().st_mtime > t for d in deps)
+    have = source_digest()
+    return "" if built_from == have else f"library build id {built_from}, sources {have}"
 
 
 def load():
@@ -130,10 +132,6 @@ def load():
                 f"{path} not found. Build it with `python -m fold_cp_ops_b200.build` (needs nvcc); "
                 "there is no PyTorch or CPU fallback for the TriMul kernels."
             )
-        if override_is_default() and _sources_newer_than(path):
-            raise TrimulLibraryError(
-                f"{path} is older than the CUDA sources next to it; rebuild it with "
-                "`python -m fold_cp_ops_b200.build` (a stale library is never loaded silently).")
         try:
             lib = C.CDLL(str(path))
         except OSError as exc:  # pragma: no cover - depends on the host
@@ -143,6 +141,11 @@ def load():
             raise TrimulLibraryError(
                 f"{path} was built from older sources: it does not export {missing}. Rebuild it with "
                 "`python -m fold_cp_ops_b200.build`.")
+        stale = _stale_reason(lib)
+        if stale:
+            raise TrimulLibraryError(
+                f"{path} was not built from the CUDA sources next to it ({stale}); rebuild it with "
+                "`python -m fold_cp_ops_b200.build` (a stale library is never loaded silently).")
         vp, i32, u64, f32p = C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p
         lib.trimul_sm100_last_error.restype = C.c_char_p
         lib.trimul_sm100_last_error.argtypes = []

@@ -30,6 +30,19 @@ NVCC_FLAGS = (
 )
 
 
+def source_digest() -> str:
+    """sha256 over the CUDA sources, their headers and the public header, in a fixed order.  Compiled into
+    the library (``trimul_sm100_build_id``) so that the loader can tell a library built from other sources
+    without relying on file times, which a copy of the tree does not preserve."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for f in [CSRC / s for s in SOURCES + HEADERS] + [PKG_DIR.parent / "include" / "trimul_sm100.h"]:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()[:32]
+
+
 def _nvcc() -> str:
     cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(cand).exists():
@@ -54,6 +67,7 @@ def build(verbose: bool = False, ptxas_info: bool = False, ablate: int = 0) -> P
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
     out = LIB_PATH if not ablate else PKG_DIR / f"libtrimul_sm100_ablate{int(ablate)}.so"
     extra = [f"-DTRIMUL_ABLATE={int(ablate)}"] if ablate else []
+    extra.append(f'-DTRIMUL_BUILD_ID="{source_digest()}"')
     cmd = [_nvcc(), *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if ptxas_info else []), "-o", str(out), *srcs]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)

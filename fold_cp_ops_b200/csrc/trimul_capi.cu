@@ -484,6 +484,11 @@ extern "C" {
 
 const char* trimul_sm100_last_error(void) { return g_err; }
 
+#ifndef TRIMUL_BUILD_ID
+#define TRIMUL_BUILD_ID "unknown"
+#endif
+const char* trimul_sm100_build_id(void) { return TRIMUL_BUILD_ID; }
+
 int trimul_sm100_query(int device, trimul_caps_t* out) {
   if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "caps is NULL");
   cudaDeviceProp prop;

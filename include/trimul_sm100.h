@@ -147,6 +147,10 @@ int trimul_sm100_query(int device, trimul_caps_t* out);
 int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* out);
 int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out);
 const char* trimul_sm100_last_error(void);
+/* Digest of the sources this library was compiled from (set by the build script; "unknown" for a hand
+ * build).  The Python loader compares it with the sources beside the library and refuses a stale one.
+ * No counterpart in the reference, whose kernels are JIT-compiled from the installed sources. */
+const char* trimul_sm100_build_id(void);
 
 /* Pack the input-side weights once at construction: rows of p_in / g_in / g_out (each row-major
  * (out, in), bf16) are regrouped into 4d/256 gated chunks of 256 rows (128 projection rows of a --

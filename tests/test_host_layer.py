@@ -271,6 +271,28 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, sym), sym
 
 
+def test_loader_refuses_a_library_built_from_other_sources(monkeypatch):
+    """The loader compares the digest compiled into the library with the sources beside it (file times do
+    not survive a copy of the tree): the real library matches, a library reporting another digest is stale."""
+    from fold_cp_ops_b200 import build
+
+    real = ctypes.CDLL(str(_lib.library_path()))
+    assert _lib._stale_reason(real) == ""
+    real.trimul_sm100_build_id.restype = ctypes.c_char_p
+    assert real.trimul_sm100_build_id().decode() == build.source_digest()
+
+    class Other:
+        class trimul_sm100_build_id:  # noqa: N801 - mimics a ctypes function object
+            restype = argtypes = None
+
+            def __new__(cls):
+                return b"0123456789abcdef0123456789abcdef"
+
+    assert "library build id 0123" in _lib._stale_reason(Other)
+    monkeypatch.setenv("CPO_TRIMUL_LIB", str(_lib.library_path()))   # an explicitly chosen library is not second-guessed
+    assert _lib._stale_reason(Other) == ""
+
+
 def test_geometry_refusals_come_back_as_value_errors():
     for kw, pat in ((dict(n=12), "multiple of 8"), (dict(d=64), "not supported"), (dict(cp0=3, n=24), "must divide"),
                     (dict(cp0=2, cp1=2, rank=7), "rank"), (dict(cp0=4, cp1=4), "ranks"),
