@@ -433,22 +433,32 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
     }
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
-    uint32_t buf = 0, buf_phase = 0;
-    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    // every row of this warp is requested before any is used: 16 rows in flight per warp
+    auto request_rows = [&](long t, uint4 (&dst)[PASSES]) {
       const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
       const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
-      // every row of this warp is requested before any is used: 16 x 512 B in flight per warp
-      uint4 raw[PASSES];
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {
         const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
         const int w = tc.w0 + r;
         if (w < p.n_walk && !(kAblate & 2)) {
-          raw[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
+          dst[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
         } else {
-          raw[ps] = make_uint4(0, 0, 0, 0);
+          dst[ps] = make_uint4(0, 0, 0, 0);
         }
       }
+    };
+    // When a tile's rows fit in half of the register budget (D = 128: eight 16-byte loads per lane) the
+    // rows of the NEXT tile are requested before this tile is written to shared memory, so the HBM latency
+    // of a tile is hidden behind the normalisation and hand-off of the one before it; at D = 256 one tile
+    // fills the registers, and the single operand buffer gives the loads a whole MMA phase anyway.
+    constexpr bool kPrefetch = PASSES <= 8;
+    uint4 raw[PASSES];
+    uint4 ahead[kPrefetch ? PASSES : 1];
+    bool have_rows = false;
+    uint32_t buf = 0, buf_phase = 0;
+    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      if (!have_rows) request_rows(t, raw);
       // normalise in registers while the tensor core still reads the previous tile
 #pragma unroll
       for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
@@ -475,6 +485,10 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
         raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
       }
+      if constexpr (kPrefetch) {
+        have_rows = t + gridDim.x < total_tiles;
+        if (have_rows) request_rows(t + gridDim.x, ahead);
+      }
       bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -492,6 +506,12 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
+      if constexpr (kPrefetch) {
+        if (have_rows) {
+#pragma unroll
+          for (int ps = 0; ps < PASSES; ++ps) raw[ps] = ahead[ps];
+        }
+      }
       if (++buf == C::kABufs) {
         buf = 0;
         buf_phase ^= 1;
