@@ -43,6 +43,9 @@ WORKLOADS = {
     "mesh2x4_incoming_pad_n4096_d256": dict(B=1, N=4096, D=256, direction="incoming", mesh="2d", mask="pad"),
     "large_n8192_d128": dict(B=2, N=8192, D=128, direction="outgoing", mesh="1d", mask="ones"),
     "single_n1024_d128": dict(B=1, N=1024, D=128, direction="outgoing", mesh="1d", mask="ones"),
+    # the wide feature widths the reference pins at cp=1 (N=2048; 32.7 / 43.9 ms on H100)
+    "wide_n2048_d384": dict(B=1, N=2048, D=384, direction="outgoing", mesh="1d", mask="ones"),
+    "wide_n2048_d512": dict(B=1, N=2048, D=512, direction="outgoing", mesh="1d", mask="ones"),
     "smoke_n256_d128": dict(B=1, N=256, D=128, direction="outgoing", mesh="1d", mask="ones"),
     # small cases for ncu captures (inputs > L2, < 2 GB on the device)
     "profile_n1024_d256": dict(B=1, N=1024, D=256, direction="outgoing", mesh="1d", mask="ones"),

@@ -59,29 +59,38 @@ constexpr int kFwdWarp = 3;              // control warp whose lane 0 forwards s
 // columns followed by the 128 gate columns of the same channels, N = 256 -- the MMA shape that
 // keeps the tensor core off the shared-memory bandwidth limit (a 128 x 128 x 16 MMA reads as many
 // operand bytes as it has clocks for).  D = 256: a_lo, a_hi, b_lo, b_hi, gate (N = 256);
-// D = 128: a, b, gate (N = 128).
+// D = 128: a, b, gate (N = 128).  Wide rows (D = 384, 512): six / eight gated chunks and the output gate
+// in chunks of 128 columns; the operand tile alone is 96 / 128 KB, so the weight ring has two stages, the
+// tile is single-buffered and D = 512 has ONE staging buffer (each chunk's stores drain before the next
+// chunk is staged) -- the same pipeline with less slack, not a different kernel.
 template <int D>
 struct Cfg {
+  static constexpr bool kWide = D > 256;
   static constexpr int CH = 128;                // channels per gated chunk
   static constexpr int kChunkN = 2 * CH;        // columns of a gated chunk (also the accumulator stride in TMEM)
   static constexpr int kGated = 2 * D / CH;     // gated chunks per tile
   static constexpr int kPerHalf = kGated / 2;   // gated chunks of a (and of b)
-  static constexpr int kNumChunks = kGated + 1; // + the output-gate chunk (N = D)
+  static constexpr int kGateN = kWide ? 128 : D;         // columns of one output-gate chunk
+  static constexpr int kGateChunks = D / kGateN;         // output-gate chunks per tile
+  static constexpr int kNumChunks = kGated + kGateChunks;
   static constexpr int KB = D / 64;             // 64-wide K blocks
   static constexpr int kABytes = BM * D * 2;    // one operand tile
   static constexpr int kKBlockBytes = BM * 128; // one K block of the operand tile
-  static constexpr int kWBoxRows = D;           // rows one weight TMA box brings (the packed matrix has 5 D rows)
+  static constexpr int kWBoxRows = kWide ? 128 : D;   // rows one weight TMA box brings (the packed matrix has 5 D rows)
   static constexpr int kWStageBytes = kChunkN * 128;  // one stage: up to 256 weight rows x 64 k
-  static constexpr int kWStages = 3;
-  static constexpr int kABufs = (D == 256) ? 1 : 2;
+  static constexpr int kWStages = kWide ? 2 : 3;
+  static constexpr int kABufs = (D == 128) ? 2 : 1;
   static constexpr int kTmemCols = 512;
   static constexpr int kHalfBytes = CH * 128;        // one token half of a staged a|b chunk: CH channel rows of 64 tokens
   static constexpr int kStageBuf = 2 * kHalfBytes;   // one staging buffer: CH channels x 128 tokens (a|b chunk), or two gate boxes
   static constexpr int kGateBoxBytes = BM * 128;     // gate box: 128 tokens x 64 channels, 128-byte swizzle
-  static constexpr int kStBufs = 2;                  // staging buffers (two to four; more did not pay at D = 128)
+  static constexpr int kStBufs = (D == 512) ? 1 : 2; // staging buffers (two to four; more did not pay at D = 128)
   static constexpr int kBoxesPerBuf = kStageBuf / kGateBoxBytes;  // gate boxes one buffer holds
-  static constexpr int kGateUses = (D / 64) / kBoxesPerBuf;       // staging buffers the gate chunk fills
+  static constexpr int kGateUses = (kGateN / 64) / kBoxesPerBuf;  // staging buffers one output-gate chunk fills
   static constexpr int kTileBytes = kABufs * kABytes + kWStages * kWStageBytes + kStBufs * kStageBuf;
+  // first row of chunk c in the packed weight / bias arrays, and its number of columns
+  static constexpr __host__ __device__ int chunk_row0(int c) { return c < kGated ? c * kChunkN : 4 * D + (c - kGated) * kGateN; }
+  static constexpr __host__ __device__ int chunk_cols(int c) { return c < kGated ? kChunkN : kGateN; }
 };
 
 template <int D>
@@ -197,10 +206,10 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
 // Order in which a CTA walks the five column chunks of a tile.  The four gated chunks (a_lo, a_hi,
 // b_lo, b_hi) belong to different owner ranks; CTAs start them at different points of the cycle so
 // that, at any moment, the stores of the whole grid are spread over all owners (and all NVLink
-// directions) instead of everyone sending to the same half of the ranks.  The gate chunk stays last.
+// directions) instead of everyone sending to the same half of the ranks.  The gate chunks stay last.
 template <int GATED>
 __device__ __forceinline__ int chunk_at(int step, int rot) {
-  return step < GATED ? ((step + rot) & (GATED - 1)) : GATED;
+  return step < GATED ? (step + rot) % GATED : step;
 }
 
 struct TileCoord {
@@ -235,7 +244,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   const int tiles_per_line = (p.n_walk + BM - 1) / BM;
   const long total_tiles = static_cast<long>(p.batch) * p.n_lines * tiles_per_line;
-  const int rot = p.rotate_chunks ? static_cast<int>(blockIdx.x & 3) : 0;  // see chunk_at
+  const int rot = p.rotate_chunks ? static_cast<int>(blockIdx.x % C::kGated) : 0;  // see chunk_at
 
   if (threadIdx.x == 0) {
     timeline_min(p.timeline, kTlFrontStart);
@@ -290,13 +299,13 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               ps.advance(C::kWStages);
               continue;
             }
-            // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunk the last D rows
-            const int rows = c < C::kGated ? C::kChunkN : D;
+            // a gated chunk is rows [256 c, 256 c + 256) of the packed matrix, the gate chunks the last D rows
+            const int rows = C::chunk_cols(c);
             ctl->armed[ps.stage] = ps.phase;
             sm100::mbar_arrive_expect_tx(&ctl->w_full[ps.stage], rows * 128);
             for (int r0 = 0; r0 < rows; r0 += C::kWBoxRows) {
               sm100::tma_load_2d(w_tiles + ps.stage * C::kWStageBytes + r0 * 128, &tmW, &ctl->w_full[ps.stage], kb * 64,
-                                 c * C::kChunkN + r0);
+                                 C::chunk_row0(c) + r0);
             }
             ps.advance(C::kWStages);
           }
@@ -305,7 +314,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- UMMA issuer
       constexpr uint32_t idesc_gated = sm100::umma_idesc_bf16_f32(BM, C::kChunkN);
-      constexpr uint32_t idesc_gate = sm100::umma_idesc_bf16_f32(BM, D);
+      constexpr uint32_t idesc_gate = sm100::umma_idesc_bf16_f32(BM, C::kGateN);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
@@ -358,14 +367,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
     } else if (warp == kFwdWarp && lane == 0) {
       // ---------------------------------------------------------- forwarder (TMA stores of staged tiles)
-      // Six buffer uses per tile: four a|b chunks (one buffer each) and the gate tile (two buffers).
+      // Buffer uses per tile: one per a|b chunk and kGateUses per output-gate chunk (D = 256: 4 + 2).
       // Use u lives in buffer u % kStBufs, phase (u / kStBufs) & 1; every use is one bulk group.  A
       // buffer is handed back when its group has been read; with more than two buffers the forwarder
       // waits only for the group kStBufs - 2 behind the newest, so it never stalls on its own last
       // stores.
       constexpr uint32_t NB = C::kStBufs;
-      const int d_loc_mask = (1 << p.d_loc_log2) - 1;
-      const int d_loc_n = 1 << p.d_loc_log2;
+      constexpr uint32_t kLag = NB >= 2 ? NB - 2 : 0;   // bulk groups that may still read their buffer
+      const int d_loc_n = p.d_loc;
       uint32_t use = 0;
       bool ok = true, stamped = false;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -392,8 +401,9 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll 1
               for (int k = 0; k < ((kAblate & 8) ? 0 : C::CH / 16); ++k) {
                 const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
-                const CUtensorMap* map = &om.ab[d >> p.d_loc_log2];
-                const int plane = h * d_loc_n + (d & d_loc_mask);
+                const int owner = d / d_loc_n;
+                const CUtensorMap* map = &om.ab[owner];
+                const int plane = h * d_loc_n + (d - owner * d_loc_n);
                 // sixteen channel rows of each token half: (64 tokens, 16 channels) boxes, 128-byte rows
                 sm100::tma_store_4d(map, src + k * 16 * 128, dst_x, dst_y, tc.b, plane);
                 sm100::tma_store_4d(map, src + C::kHalfBytes + k * 16 * 128, dst_x + kHalfTokens, dst_y, tc.b, plane);
@@ -403,13 +413,13 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               const int cl = p.gate_walk_dim == 1 ? tc.line : tc.w0;
 #pragma unroll 1
               for (int j = 0; j < ((kAblate & 8) ? 0 : C::kBoxesPerBuf); ++j) {
-                const int jb = u * C::kBoxesPerBuf + j;  // gate box: channels [64 jb, 64 jb + 64)
+                const int jb = (c - C::kGated) * (C::kGateN / 64) + u * C::kBoxesPerBuf + j;  // gate box: channels [64 jb, 64 jb + 64)
                 sm100::tma_store_4d(&om.gate, src + j * C::kGateBoxBytes, jb * 64, cw, cl, tc.b);
               }
             }
             sm100::tma_store_commit();
-            sm100::tma_store_wait_read<NB - 2>();  // every group but the newest NB - 2 has read its buffer
-            if (use + 2 >= NB) sm100::mbar_arrive(&ctl->st_free[(use + 2 - NB) % NB]);
+            sm100::tma_store_wait_read<kLag>();  // every group but the newest kLag has read its buffer
+            if (kLag == 0 || use >= kLag) sm100::mbar_arrive(&ctl->st_free[(use - kLag) % NB]);
           }
         }
       }
@@ -419,102 +429,198 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   } else if (warp >= kLnWarp0) {
     // ------------------------------------------------------------ LayerNorm prologue (8 warps)
     sm100::setmaxnreg_inc<104>();
-    constexpr int CPR = D / 8;        // 16-byte chunks per row
-    constexpr int RPP = 32 / CPR;     // rows one warp-wide load covers
-    constexpr int ROWS_PER_WARP = 16;
-    constexpr int PASSES = ROWS_PER_WARP / RPP;
     const int lw = warp - kLnWarp0;
-    const int chunk = lane % CPR;
-    const int sub = lane / CPR;
-    float gam[8], bet[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      gam[e] = p.ln_w[chunk * 8 + e];
-      bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
-    }
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
-    // every row of this warp is requested before any is used: 16 rows in flight per warp
-    auto request_rows = [&](long t, uint4 (&dst)[PASSES]) {
-      const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
-      const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+    if constexpr (C::kWide) {
+      // Rows of 768 / 1024 bytes: a lane owns the 16-byte chunks `lane` and `lane + 32` of a row (the second
+      // one only exists for lane + 32 < D / 8), a warp normalises its sixteen rows in four batches of four.
+      constexpr int CPR = D / 8;
+      constexpr int ROWS_PER_WARP = 16, RB = 4;
+      const int c0 = lane, c1 = lane + 32;
+      const bool has1 = c1 < CPR;
+      float gam[16], bet[16];
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
-        const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
-        const int w = tc.w0 + r;
-        if (w < p.n_walk && !(kAblate & 2)) {
-          dst[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
-        } else {
-          dst[ps] = make_uint4(0, 0, 0, 0);
+      for (int e = 0; e < 8; ++e) {
+        gam[e] = p.ln_w[c0 * 8 + e];
+        bet[e] = p.ln_b ? p.ln_b[c0 * 8 + e] : 0.0f;
+        gam[8 + e] = has1 ? p.ln_w[c1 * 8 + e] : 0.0f;
+        bet[8 + e] = (has1 && p.ln_b) ? p.ln_b[c1 * 8 + e] : 0.0f;
+      }
+      uint32_t buf_phase = 0;
+      for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
+        const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+        bool ok = true;
+#pragma unroll 1
+        for (int rb = 0; rb < ROWS_PER_WARP / RB && ok; ++rb) {
+          uint4 raw[RB][2];
+#pragma unroll
+          for (int i = 0; i < RB; ++i) {
+            const int w = tc.w0 + lw * ROWS_PER_WARP + rb * RB + i;
+            const uint8_t* row = xb + (row0 + static_cast<long>(w) * p.walk_rows) * D * 2;
+            const bool live = w < p.n_walk && !(kAblate & 2);
+            raw[i][0] = live ? ldg_nc_v4(row + c0 * 16) : make_uint4(0, 0, 0, 0);
+            raw[i][1] = (live && has1) ? ldg_nc_v4(row + c1 * 16) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < RB; ++i) {
+            float v[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              v[8 * h + 0] = sm100::bf16_lo(raw[i][h].x); v[8 * h + 1] = sm100::bf16_hi(raw[i][h].x);
+              v[8 * h + 2] = sm100::bf16_lo(raw[i][h].y); v[8 * h + 3] = sm100::bf16_hi(raw[i][h].y);
+              v[8 * h + 4] = sm100::bf16_lo(raw[i][h].z); v[8 * h + 5] = sm100::bf16_hi(raw[i][h].z);
+              v[8 * h + 6] = sm100::bf16_lo(raw[i][h].w); v[8 * h + 7] = sm100::bf16_hi(raw[i][h].w);
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) sum += v[e];
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float mean = sum * (1.0f / D);
+            float q = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              v[e] -= mean;
+              if (e < 8 || has1) q = fmaf(v[e], v[e], q);
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+            const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const float* g = gam + 8 * h;
+              const float* bt = bet + 8 * h;
+              const float* vv = v + 8 * h;
+              raw[i][h].x = sm100::pack_bf16x2(fmaf(vv[0] * rstd, g[0], bt[0]), fmaf(vv[1] * rstd, g[1], bt[1]));
+              raw[i][h].y = sm100::pack_bf16x2(fmaf(vv[2] * rstd, g[2], bt[2]), fmaf(vv[3] * rstd, g[3], bt[3]));
+              raw[i][h].z = sm100::pack_bf16x2(fmaf(vv[4] * rstd, g[4], bt[4]), fmaf(vv[5] * rstd, g[5], bt[5]));
+              raw[i][h].w = sm100::pack_bf16x2(fmaf(vv[6] * rstd, g[6], bt[6]), fmaf(vv[7] * rstd, g[7], bt[7]));
+            }
+          }
+          if (rb == 0) {  // the tensor core must have released the (single) operand tile before the first write
+            ok = sm100::mbar_wait(&ctl->x_empty[0], buf_phase ^ 1, abort_flag, tmo);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+              report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
+              break;
+            }
+          }
+          if (!(kAblate & 2)) {
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+              const int r = lw * ROWS_PER_WARP + rb * RB + i;
+              // K-major, 128-byte swizzle: K block (chunk / 8), row r, 16-byte slot (chunk % 8) ^ (r % 8)
+              *reinterpret_cast<uint4*>(a_tiles + (c0 >> 3) * C::kKBlockBytes + r * 128 + (((c0 & 7) ^ (r & 7)) << 4)) =
+                  raw[i][0];
+              if (has1)
+                *reinterpret_cast<uint4*>(a_tiles + (c1 >> 3) * C::kKBlockBytes + r * 128 + (((c1 & 7) ^ (r & 7)) << 4)) =
+                    raw[i][1];
+            }
+          }
         }
-      }
-    };
-    // When a tile's rows fit in half of the register budget (D = 128: eight 16-byte loads per lane) the
-    // rows of the NEXT tile are requested before this tile is written to shared memory, so the HBM latency
-    // of a tile is hidden behind the normalisation and hand-off of the one before it; at D = 256 one tile
-    // fills the registers, and the single operand buffer gives the loads a whole MMA phase anyway.
-    constexpr bool kPrefetch = PASSES <= 8;
-    uint4 raw[PASSES];
-    uint4 ahead[kPrefetch ? PASSES : 1];
-    bool have_rows = false;
-    uint32_t buf = 0, buf_phase = 0;
-    for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      if (!have_rows) request_rows(t, raw);
-      // normalise in registers while the tensor core still reads the previous tile
-#pragma unroll
-      for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
-        float v[8];
-        v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
-        v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
-        v[4] = sm100::bf16_lo(raw[ps].z); v[5] = sm100::bf16_hi(raw[ps].z);
-        v[6] = sm100::bf16_lo(raw[ps].w); v[7] = sm100::bf16_hi(raw[ps].w);
-        float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-#pragma unroll
-        for (int o = CPR / 2; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const float mean = s * (1.0f / D);
-        float q = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          v[e] -= mean;
-          q = fmaf(v[e], v[e], q);
-        }
-#pragma unroll
-        for (int o = CPR / 2; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-        const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
-        raw[ps].x = sm100::pack_bf16x2(fmaf(v[0] * rstd, gam[0], bet[0]), fmaf(v[1] * rstd, gam[1], bet[1]));
-        raw[ps].y = sm100::pack_bf16x2(fmaf(v[2] * rstd, gam[2], bet[2]), fmaf(v[3] * rstd, gam[3], bet[3]));
-        raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
-        raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
-      }
-      if constexpr (kPrefetch) {
-        have_rows = t + gridDim.x < total_tiles;
-        if (have_rows) request_rows(t + gridDim.x, ahead);
-      }
-      bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
-        break;
-      }
-      uint8_t* a_tile = a_tiles + buf * C::kABytes;
-#pragma unroll
-      for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
-        const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
-        // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
-        const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(a_tile + off) = raw[ps];
-      }
-      sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
-      if constexpr (kPrefetch) {
-        if (have_rows) {
-#pragma unroll
-          for (int ps = 0; ps < PASSES; ++ps) raw[ps] = ahead[ps];
-        }
-      }
-      if (++buf == C::kABufs) {
-        buf = 0;
+        if (!ok) break;
+        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[0]);
         buf_phase ^= 1;
+      }
+    } else {
+      constexpr int CPR = D / 8;        // 16-byte chunks per row
+      constexpr int RPP = 32 / CPR;     // rows one warp-wide load covers
+      constexpr int ROWS_PER_WARP = 16;
+      constexpr int PASSES = ROWS_PER_WARP / RPP;
+      const int chunk = lane % CPR;
+      const int sub = lane / CPR;
+      float gam[8], bet[8];
+  #pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        gam[e] = p.ln_w[chunk * 8 + e];
+        bet[e] = p.ln_b ? p.ln_b[chunk * 8 + e] : 0.0f;
+      }
+      // every row of this warp is requested before any is used: 16 rows in flight per warp
+      auto request_rows = [&](long t, uint4 (&dst)[PASSES]) {
+        const TileCoord tc = decode_tile(t, tiles_per_line, p.n_lines);
+        const long row0 = tc.b * p.batch_rows + tc.line * p.line_rows;
+  #pragma unroll
+        for (int ps = 0; ps < PASSES; ++ps) {
+          const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
+          const int w = tc.w0 + r;
+          if (w < p.n_walk && !(kAblate & 2)) {
+            dst[ps] = ldg_nc_v4(xb + ((row0 + w * p.walk_rows) * D + chunk * 8) * 2);
+          } else {
+            dst[ps] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      };
+      // When a tile's rows fit in half of the register budget (D = 128: eight 16-byte loads per lane) the
+      // rows of the NEXT tile are requested before this tile is written to shared memory, so the HBM latency
+      // of a tile is hidden behind the normalisation and hand-off of the one before it; at D = 256 one tile
+      // fills the registers, and the single operand buffer gives the loads a whole MMA phase anyway.
+      constexpr bool kPrefetch = PASSES <= 8;
+      uint4 raw[PASSES];
+      uint4 ahead[kPrefetch ? PASSES : 1];
+      bool have_rows = false;
+      uint32_t buf = 0, buf_phase = 0;
+      for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        if (!have_rows) request_rows(t, raw);
+        // normalise in registers while the tensor core still reads the previous tile
+  #pragma unroll
+        for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
+          float v[8];
+          v[0] = sm100::bf16_lo(raw[ps].x); v[1] = sm100::bf16_hi(raw[ps].x);
+          v[2] = sm100::bf16_lo(raw[ps].y); v[3] = sm100::bf16_hi(raw[ps].y);
+          v[4] = sm100::bf16_lo(raw[ps].z); v[5] = sm100::bf16_hi(raw[ps].z);
+          v[6] = sm100::bf16_lo(raw[ps].w); v[7] = sm100::bf16_hi(raw[ps].w);
+          float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+  #pragma unroll
+          for (int o = CPR / 2; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          const float mean = s * (1.0f / D);
+          float q = 0.0f;
+  #pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[e] -= mean;
+            q = fmaf(v[e], v[e], q);
+          }
+  #pragma unroll
+          for (int o = CPR / 2; o >= 1; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+          const float rstd = rsqrtf(q * (1.0f / D) + p.eps);
+          raw[ps].x = sm100::pack_bf16x2(fmaf(v[0] * rstd, gam[0], bet[0]), fmaf(v[1] * rstd, gam[1], bet[1]));
+          raw[ps].y = sm100::pack_bf16x2(fmaf(v[2] * rstd, gam[2], bet[2]), fmaf(v[3] * rstd, gam[3], bet[3]));
+          raw[ps].z = sm100::pack_bf16x2(fmaf(v[4] * rstd, gam[4], bet[4]), fmaf(v[5] * rstd, gam[5], bet[5]));
+          raw[ps].w = sm100::pack_bf16x2(fmaf(v[6] * rstd, gam[6], bet[6]), fmaf(v[7] * rstd, gam[7], bet[7]));
+        }
+        if constexpr (kPrefetch) {
+          have_rows = t + gridDim.x < total_tiles;
+          if (have_rows) request_rows(t + gridDim.x, ahead);
+        }
+        bool ok = sm100::mbar_wait(&ctl->x_empty[buf], buf_phase ^ 1, abort_flag, tmo);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          report_timeout(p.status, kKernelGatedProj, 3, static_cast<int>(t));
+          break;
+        }
+        uint8_t* a_tile = a_tiles + buf * C::kABytes;
+  #pragma unroll
+        for (int ps = 0; ps < ((kAblate & 2) ? 0 : PASSES); ++ps) {
+          const int r = lw * ROWS_PER_WARP + ps * RPP + sub;
+          // K-major, 128-byte swizzle: K block (chunk/8), row r, 16-byte slot (chunk%8) ^ (r%8)
+          const uint32_t off = (chunk >> 3) * C::kKBlockBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(a_tile + off) = raw[ps];
+        }
+        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl->xn_ready[buf]);
+        if constexpr (kPrefetch) {
+          if (have_rows) {
+  #pragma unroll
+            for (int ps = 0; ps < PASSES; ++ps) raw[ps] = ahead[ps];
+          }
+        }
+        if (++buf == C::kABufs) {
+          buf = 0;
+          buf_phase ^= 1;
+        }
       }
     }
   } else {
@@ -578,7 +684,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           constexpr int CW = C::CH / 4;   // channels of the chunk this warp handles
           constexpr int NS = CW / 16;     // in 16-channel sub-groups
           const int colw = part * CW;
-          const float* bias_p0 = p.bias + c * C::kChunkN + colw;
+          const float* bias_p0 = p.bias + C::chunk_row0(c) + colw;
           const uint32_t trow_hi = trow + (16u << 16);   // TMEM lanes 16-31 of the quarter
           // staged layout: token half (quarter / 2), channel row, 16-byte slot of eight tokens
           // (quarter % 2) * 4 + tile, XOR-swizzled with the row as the store descriptor expects
@@ -608,11 +714,11 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
         } else {
           // output-gate chunk: sigmoid only, token-major, into (128 token x 64 channel) boxes
-          constexpr int GW = D / 4;
+          constexpr int GW = C::kGateN / 4;
           constexpr int NS = GW / 16;
           const int colw = part * GW;
-          const float* bias_g0 = p.bias + 4 * D + colw;
-          const int jb = colw >> 6;  // gate box of this warp's columns; boxes fill the chunk's two buffers in order
+          const float* bias_g0 = p.bias + C::chunk_row0(c) + colw;
+          const int jb = colw >> 6;  // gate box of this warp's columns inside the chunk; boxes fill the chunk's buffers in order
           uint8_t* box = st_tiles + ((use + jb / C::kBoxesPerBuf) % NB) * C::kStageBuf +
                          (jb % C::kBoxesPerBuf) * C::kGateBoxBytes;
           const int slot_base = (colw & 63) >> 3;
@@ -668,6 +774,8 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 int gated_proj_smem_bytes(int D) {
   if (D == 128) return smem_bytes<128>();
   if (D == 256) return smem_bytes<256>();
+  if (D == 384) return smem_bytes<384>();
+  if (D == 512) return smem_bytes<512>();
   return -1;
 }
 
@@ -689,6 +797,8 @@ cudaError_t launch_gated_proj(const CUtensorMap& tmW, const GatedOutMaps& maps, 
                               cudaStream_t stream) {
   if (args.D == 128) return launch_t<128>(tmW, maps, args, num_sms, stream);
   if (args.D == 256) return launch_t<256>(tmW, maps, args, num_sms, stream);
+  if (args.D == 384) return launch_t<384>(tmW, maps, args, num_sms, stream);
+  if (args.D == 512) return launch_t<512>(tmW, maps, args, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

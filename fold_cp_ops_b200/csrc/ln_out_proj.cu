@@ -37,17 +37,29 @@ constexpr int kEpiWarp0 = 4;
 constexpr int kStatWarp0 = 12;
 constexpr int kTriBytes = 2 * 64 * 128;   // one K block of the tile: two token blocks x 64 channels x 128 B
 constexpr int kBoxBytes = BM * 128;       // gate / out box: 128 tokens x 64 channels
-constexpr int kBoxSlots = 4;
+constexpr int kMaxBoxSlots = 4;
 
+// D = 128 / 256: two accumulators (the epilogue of tile t overlaps the MMAs of tile t + 1), 3-4 ring stages.
+// D = 384 / 512: one accumulator fills most of TMEM (D columns) and a K block of the folded weights is
+// 48-64 KB, so the ring has two stages, the tiles are serialised on the single accumulator and every MMA
+// step is issued in column chunks of at most 256.
 template <int D>
 struct Cfg {
   static constexpr int KB = D / 64;                // K blocks per tile
   static constexpr int NBT = D / 64;               // gate / out boxes per tile
+  static constexpr int NBS = NBT / 2;              // boxes per channel half (one half per epilogue warp set)
   static constexpr int kWBytes = D * 128;          // one K block of the folded weights: D rows x 64 k
+  static constexpr int kWBoxRows = (D <= 256) ? D : 128;  // rows one weight TMA box brings
   static constexpr int kStageBytes = kTriBytes + kWBytes;
-  static constexpr int kStages = (D == 256) ? 3 : 4;
+  static constexpr int kStages = (D > 256) ? 2 : ((D == 256) ? 3 : 4);
+  static constexpr int kAccs = (2 * D <= 512) ? 2 : 1;
   static constexpr int kTmemCols = (2 * D <= 256) ? 256 : 512;
+  static constexpr int kBoxSlots = (D == 512) ? 3 : 4;
   static constexpr int kTileBytes = kStages * kStageBytes + kBoxSlots * kBoxBytes;
+  // Boxes are loaded, combined and stored in the order the two channel halves consume them: the first
+  // box of each half, then the second of each, ...; position j of that order holds box (j & 1) * NBS + j / 2.
+  static constexpr __host__ __device__ int box_at(int j) { return (j & 1) * NBS + (j >> 1); }
+  static constexpr __host__ __device__ int pos_of(int jb) { return 2 * (jb % NBS) + jb / NBS; }
 };
 
 template <int D>
@@ -58,13 +70,13 @@ struct SmemCtl {
   uint64_t tmem_empty[2];
   uint64_t red_bar[2];
   uint64_t stats_ready[2];
-  uint64_t g_full[kBoxSlots];   // gate box landed (TMA transaction bytes)
-  uint64_t o_full[kBoxSlots];   // box overwritten with the result by the four warps that own it
-  uint64_t g_free[kBoxSlots];   // result read by its bulk store: the slot may be refilled
+  uint64_t g_full[kMaxBoxSlots];   // gate box landed (TMA transaction bytes)
+  uint64_t o_full[kMaxBoxSlots];   // box overwritten with the result by the four warps that own it
+  uint64_t g_free[kMaxBoxSlots];   // result read by its bulk store: the slot may be refilled
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   volatile uint32_t armed[Cfg<D>::kStages];
-  volatile uint32_t g_armed[kBoxSlots];
+  volatile uint32_t g_armed[kMaxBoxSlots];
   alignas(16) float2 red[2][4][BM];   // [tile parity][channel subgroup][token] = (mean, M2) over D/4 channels
   float2 stat[2][BM];                 // [accumulator][token] = (rstd, -mean * rstd)
   float2 cd[D];                       // (c[n], d[n]) of the folded projection
@@ -87,6 +99,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = tiles;                                   // kStages x [tri K block | weight K block]
   uint8_t* boxes = tiles + C::kStages * C::kStageBytes;    // kBoxSlots x kBoxBytes
+  constexpr int kBoxSlots = C::kBoxSlots;
   SmemCtl<D>* ctl = reinterpret_cast<SmemCtl<D>*>(tiles + C::kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -149,7 +162,9 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           // (tokens, channels) boxes of 64 x 64; a block past the last token is zero-filled
           sm100::tma_load_2d(st, &tmT, &ctl->full[ps.stage], static_cast<int>(m0), kb * 64);
           sm100::tma_load_2d(st + kTriBytes / 2, &tmT, &ctl->full[ps.stage], static_cast<int>(m0 + 64), kb * 64);
-          sm100::tma_load_2d(st + kTriBytes, &tmW, &ctl->full[ps.stage], kb * 64, 0);
+#pragma unroll
+          for (int n0 = 0; n0 < D; n0 += C::kWBoxRows)
+            sm100::tma_load_2d(st + kTriBytes + n0 * 128, &tmW, &ctl->full[ps.stage], kb * 64, n0);
           ps.advance(C::kStages);
         }
       }
@@ -158,7 +173,10 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     // ------------------------------------------------------------ UMMA issuer
     if (lane == 0 && my_tiles > 0) {
       // A: raw tile, token-major (MN-major); B: folded weights, K-major, all D output channels
-      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, D) | (1u << 15);
+      constexpr int kN0 = D < 256 ? D : 256;   // column chunks of one MMA step: kN0 and, for D > 256, the rest
+      constexpr int kN1 = D - kN0;
+      constexpr uint32_t idesc = sm100::umma_idesc_bf16_f32(BM, kN0) | (1u << 15);
+      constexpr uint32_t idesc1 = sm100::umma_idesc_bf16_f32(BM, kN1 > 0 ? kN1 : 16) | (1u << 15);
       PipeState ps{0, 0};
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
@@ -183,13 +201,16 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             // tile: 16 channels per MMA = 2 KB; token blocks of 64 are kTriBytes/2 apart, 8-channel groups 1024 B
             const uint64_t da = sm100::umma_desc_mnmajor_sw128(a_addr + k4 * 2048, kTriBytes / 2, 1024);
             sm100::umma_bf16_ss(d_tmem, da, db + 2 * k4, idesc, (kb | k4) != 0);
+            if constexpr (kN1 > 0) {  // weight rows [256, D): 256 rows x 128 B further into the stage
+              sm100::umma_bf16_ss(d_tmem + kN0, da, db + ((kN0 * 128) >> 4) + 2 * k4, idesc1, (kb | k4) != 0);
+            }
           }
           sm100::umma_commit(&ctl->empty[ps.stage]);
           ps.advance(C::kStages);
         }
         if (!ok) break;
         sm100::umma_commit(&ctl->tmem_full[acc]);
-        if (++acc == 2) {
+        if (++acc == C::kAccs) {
           acc = 0;
           acc_phase ^= 1;
         }
@@ -203,10 +224,9 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       bool ok = true;
       for (long it = 0; it < my_tiles && ok; ++it) {
         const long m0 = (blockIdx.x + it * gridDim.x) * BM;
-        // boxes in the order the two channel halves consume them (first box of each half first)
         for (int j = 0; j < C::NBT; ++j) {
-          const int jb = (C::NBT == 4) ? ((j & 1) * 2 + (j >> 1)) : j;
-          const uint32_t sq = seq + jb;
+          const int jb = C::box_at(j);
+          const uint32_t sq = seq + j;
           const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
           if (!sm100::mbar_wait(&ctl->g_free[slot], ph ^ 1, abort_flag, tmo)) {
             report_timeout(p.status, kKernelOutProj, 6, jb);
@@ -228,10 +248,9 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       for (long it = 0; it < my_tiles && ok; ++it) {
         const long m0 = (blockIdx.x + it * gridDim.x) * BM;
         // the two channel halves finish their boxes side by side: take them in completion order
-        // (first box of each half, then the second), which is also seq order for D = 128
         for (int j = 0; j < C::NBT; ++j) {
-          const int jb = (C::NBT == 4) ? ((j & 1) * 2 + (j >> 1)) : j;
-          const uint32_t sq = seq + jb;
+          const int jb = C::box_at(j);
+          const uint32_t sq = seq + j;
           const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
           if (!sm100::mbar_wait(&ctl->o_full[slot], ph, abort_flag, tmo)) {
             report_timeout(p.status, kKernelOutProj, 7, jb);
@@ -348,7 +367,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (lane == 0) sm100::mbar_arrive(&ctl->stats_ready[acc]);
       }
       par ^= 1;
-      if (++acc == 2) {
+      if (++acc == C::kAccs) {
         acc = 0;
         acc_phase ^= 1;
       }
@@ -380,7 +399,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < NBS; ++i) {
         const int jb = set * NBS + i;
-        const uint32_t sq = seq0 + jb;
+        const uint32_t sq = seq0 + C::pos_of(jb);
         const uint32_t slot = sq % kBoxSlots, ph = (sq / kBoxSlots) & 1;
         ok = sm100::mbar_wait(&ctl->g_full[slot], ph, abort_flag, tmo);
         ok = __all_sync(0xffffffffu, ok);
@@ -426,7 +445,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       sm100::tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl->tmem_empty[acc]);
-      if (++acc == 2) {
+      if (++acc == C::kAccs) {
         acc = 0;
         acc_phase ^= 1;
       }
@@ -468,6 +487,8 @@ out_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 int out_proj_smem_bytes(int D) {
   if (D == 128) return smem_bytes<128>();
   if (D == 256) return smem_bytes<256>();
+  if (D == 384) return smem_bytes<384>();
+  if (D == 512) return smem_bytes<512>();
   return -1;
 }
 
@@ -488,6 +509,8 @@ cudaError_t launch_out_proj(const CUtensorMap& tmW, const CUtensorMap& tmT, cons
                             const CUtensorMap& tmO, const OutProjArgs& args, int num_sms, cudaStream_t stream) {
   if (args.D == 128) return launch_t<128>(tmW, tmT, tmG, tmO, args, num_sms, stream);
   if (args.D == 256) return launch_t<256>(tmW, tmT, tmG, tmO, args, num_sms, stream);
+  if (args.D == 384) return launch_t<384>(tmW, tmT, tmG, tmO, args, num_sms, stream);
+  if (args.D == 512) return launch_t<512>(tmW, tmT, tmG, tmO, args, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

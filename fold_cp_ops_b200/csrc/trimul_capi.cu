@@ -80,15 +80,15 @@ int num_sms_current() {
 }
 
 struct Derived {
-  int cp, r0, r1, ni_loc, nj_loc, d_loc, d_loc_log2;
+  int cp, r0, r1, ni_loc, nj_loc, d_loc;
   long i_off, j_off, rows;
 };
 
 int check_geom(const trimul_geom_t* g, Derived* d) {
   if (g == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "geom is NULL");
   if (g->batch < 1 || g->n < 1) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "batch and n must be >= 1");
-  if (g->d != 128 && g->d != 256)
-    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported (128 or 256)", g->d);
+  if (g->d != 128 && g->d != 256 && g->d != 384 && g->d != 512)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported (128, 256, 384 or 512)", g->d);
   if (g->cp0 < 1 || g->cp1 < 1 || g->cp0 * g->cp1 > TRIMUL_MAX_PEERS)
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "cp grid %d x %d must have 1..%d ranks", g->cp0, g->cp1,
                 TRIMUL_MAX_PEERS);
@@ -109,11 +109,8 @@ int check_geom(const trimul_geom_t* g, Derived* d) {
     return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "local token extents (%d, %d) must be multiples of 8", d->ni_loc,
                 d->nj_loc);
   d->d_loc = g->d / cp;
-  int lg = 0;
-  while ((1 << lg) < d->d_loc) ++lg;
-  if ((1 << lg) != d->d_loc)
-    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "d/cp=%d must be a power of two", d->d_loc);
-  d->d_loc_log2 = lg;
+  if (d->d_loc % 16 != 0)
+    return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "d/cp=%d must be a multiple of 16 (the reshard stores move 16 channels)", d->d_loc);
   d->i_off = static_cast<long>(d->r0) * d->ni_loc;
   d->j_off = static_cast<long>(d->r1) * d->nj_loc;
   d->rows = static_cast<long>(g->batch) * d->ni_loc * d->nj_loc;
@@ -260,7 +257,7 @@ int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(5 * D)};
     const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D <= 256 ? D : 128)};  // wide rows: 128-row boxes
     int rc = make_tmap(&out->tmW, w_packed, 2, dims, strides, box);
     if (rc != TRIMUL_OK) return rc;
   }
@@ -288,7 +285,7 @@ int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning
     if (ab_peers[s] == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "ab_peers[%d] is NULL", s);
     a.ab.ptr[s] = ab_peers[s];
   }
-  a.d_loc_log2 = d.d_loc_log2;
+  a.d_loc = d.d_loc;
   a.plane_elems = plan.plane_elems;
   a.gate_out = gate_out;
   if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
@@ -423,7 +420,7 @@ int build_out(const trimul_geom_t* geom, const Derived& d, const void* tri_local
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(D)};
     const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
-    const uint32_t box[2] = {64, static_cast<uint32_t>(D)};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(D <= 256 ? D : 128)};  // wide rows: 128-row boxes
     int rc = make_tmap(&out->tmW, w_fold, 2, dims, strides, box);
     if (rc != TRIMUL_OK) return rc;
   }
@@ -530,7 +527,7 @@ int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* 
 int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w, const void* g_out_w,
                               const float* p_in_b, const float* g_in_b, const float* g_out_b, void* w_packed,
                               float* bias_packed, trimul_stream_t stream) {
-  if (d != 128 && d != 256) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
+  if (d != 128 && d != 256 && d != 384 && d != 512) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
   if (!p_in_w || !g_in_w || !g_out_w || !w_packed || !bias_packed)
     return fail(TRIMUL_ERR_INVALID_ARGUMENT, "pack_weights: NULL weight pointer");
   pack_weights_kernel<<<5 * d, 128, 0, stream>>>(
@@ -544,7 +541,7 @@ int trimul_sm100_pack_weights(int32_t d, const void* p_in_w, const void* g_in_w,
 
 int trimul_sm100_pack_out_weights(int32_t d, const void* w_out, const float* ln_w, const float* ln_b,
                                   const float* bias_out, void* w_fold, float* cd, trimul_stream_t stream) {
-  if (d != 128 && d != 256) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
+  if (d != 128 && d != 256 && d != 384 && d != 512) return fail(TRIMUL_ERR_UNSUPPORTED_SHAPE, "feature width d=%d is not supported", d);
   if (!w_out || !ln_w || !w_fold || !cd) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "pack_out_weights: NULL pointer");
   pack_out_weights_kernel<<<d, 128, 0, stream>>>(d, static_cast<const __nv_bfloat16*>(w_out), ln_w, ln_b, bias_out,
                                                  static_cast<__nv_bfloat16*>(w_fold), cd);

@@ -35,7 +35,7 @@ struct GatedProjArgs {
   // destination of the a / b planes: ptr[s] = base of rank s's operand buffer laid out
   // (2, D_loc, B, plane_rows, plane_cols); this rank fills [dst_base + line*dst_line + w]
   PeerPtrs ab;
-  int d_loc_log2;        // log2(D / cp)
+  int d_loc;             // D / cp: channels of a (and of b) each rank contracts
   long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane

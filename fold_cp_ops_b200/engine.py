@@ -31,7 +31,7 @@ import torch
 from . import _lib
 from . import kernels as K
 
-SUPPORTED_D = (128, 256)
+SUPPORTED_D = (128, 256, 384, 512)
 
 #: default bound of the cross-rank flag waits.  Much longer than the in-kernel pipeline waits (2 s):
 #: a peer whose HOST is late (data loading, checkpoint IO, garbage collection) must be waited for, as

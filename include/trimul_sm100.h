@@ -53,7 +53,8 @@ typedef struct trimul_caps {
   int32_t supported; /* 1 when the kernels can run on this device */
 } trimul_caps_t;
 
-/* Geometry of one forward on one rank.  The global pair tensor is (batch, n, n, d); the token grid
+/* Geometry of one forward on one rank.  The global pair tensor is (batch, n, n, d), d in {128, 256, 384,
+ * 512} (other widths: TRIMUL_ERR_UNSUPPORTED_SHAPE); the token grid
  * is split cp0 x cp1 (rows x columns) and this rank is flat cp rank `rank` = r0 * cp1 + r1, the
  * row-major peer order of fold_cp_ops/distributed/pe_map.py:265-283.  cp0 = cp1 = 1 is the
  * single-GPU case. */

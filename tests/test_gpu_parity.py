@@ -68,6 +68,9 @@ def test_forward_matches_reference_golden(name, golden):
     (1, 200, 256, "all", "ones"),       # D=256, ragged
     (2, 64, 256, "none", "random"),
     (1, 256, 128, "all", "random"),     # the reference's own parity shape (N=256, D=128)
+    (1, 136, 384, "all", "random"),     # wide rows: six gated chunks, three output-gate chunks, ragged tiles
+    (2, 72, 512, "out", "pad"),         # D=512: one staging buffer, single accumulator in the output projection
+    (1, 264, 512, "all", "ones"),       # D=512, more than two tiles per line
 ])
 def test_forward_matches_oracle(direction, B, N, D, bias, mask):
     case = bf16_round_case(make_case(B, N, D, seed=1000 + N + D, bias=bias, mask=mask))
@@ -169,7 +172,7 @@ def test_incoming_is_outgoing_of_the_transposed_pair_tensor():
 # single kernels against the oracle with bf16 rounding at the same points
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("direction", ["outgoing", "incoming"])
-@pytest.mark.parametrize("D,N,B", [(128, 72, 1), (256, 40, 2)])
+@pytest.mark.parametrize("D,N,B", [(128, 72, 1), (256, 40, 2), (384, 40, 1), (512, 24, 2)])
 def test_kernel_ln_gated_proj(direction, D, N, B):
     from fold_cp_ops_b200 import kernels as K
 
@@ -236,7 +239,8 @@ def test_kernel_tri_contract_pair_form_equals_single_cta_form(N):
         K.make_tuning("triple")
 
 
-@pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0)])
+@pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0),
+                                          (384, 1, 40, 0.5), (512, 2, 24, 0.5), (512, 1, 72, 0.5)])
 def test_kernel_ln_out_proj(D, B, n, offset):
     """The folded LayerNorm (rstd * (x W'^T - mean c) + d) against an explicit fp32 LayerNorm; the last
     case shifts every token's channels far off zero (|mean| = 10 sigma), where the fold subtracts two

@@ -294,13 +294,14 @@ def test_loader_refuses_a_library_built_from_other_sources(monkeypatch):
 
 
 def test_geometry_refusals_come_back_as_value_errors():
-    for kw, pat in ((dict(n=12), "multiple of 8"), (dict(d=64), "not supported"), (dict(cp0=3, n=24), "must divide"),
+    for kw, pat in ((dict(n=12), "multiple of 8"), (dict(d=64), "not supported"), (dict(d=320), "not supported"), (dict(cp0=3, n=24), "must divide"),
                     (dict(cp0=2, cp1=2, rank=7), "rank"), (dict(cp0=4, cp1=4), "ranks"),
                     (dict(cp0=2, n=24), "multiples of 8")):
         base = dict(batch=1, n=64, d=128, direction="outgoing", eps=1e-5, cp0=1, cp1=1, rank=0)
         base.update(kw)
         with pytest.raises(ValueError, match=pat):
             K.workspace_bytes(K.make_geom(**base))
+    assert K.reshard_plan(K.make_geom(1, 64, 384, "outgoing", 1e-5, cp0=8, cp1=1, rank=5)).d_loc == 48   # not a power of two
     ws = K.workspace_bytes(K.make_geom(2, 64, 256, "incoming", 1e-5, cp0=2, cp1=2, rank=3))
     assert ws.ab_bytes == 2 * 64 * 2 * 64 * 64 * 2 and ws.tri_bytes == 256 * 2 * 32 * 32 * 2 == ws.gate_bytes
 
