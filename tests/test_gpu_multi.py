@@ -75,8 +75,9 @@ def _cp_parity(rank, world):
         coord = mesh.get_coordinate()
         r0, r1 = coord[0], (coord[1] if mesh.ndim > 1 else 0)
         for direction in ("outgoing", "incoming"):
-            for (B, N, D, bias, mask) in ((1, 64 * max(cp0, cp1), 128, "all", "random"), (2, 128, 256, "none", "pad")):
-                if D % world or N % cp0 or N % cp1 or (N // cp0) % 8 or (N // cp1) % 8:
+            for (B, N, D, bias, mask) in ((1, 64 * max(cp0, cp1), 128, "all", "random"), (2, 128, 256, "none", "pad"),
+                                          (1, 128, 384, "all", "pad")):   # wide rows; D / cp is not a power of two
+                if D % world or (D // world) % 16 or N % cp0 or N % cp1 or (N // cp0) % 8 or (N // cp1) % 8:
                     continue
                 case = bf16_round_case(make_case(B, N, D, seed=20260821 + N + D, bias=bias, mask=mask))
                 ref = trimul_oracle(case["x"], direction, case["mask"], **weights_of(case))
