@@ -51,6 +51,7 @@ WORKLOADS = {
     "profile_n1024_d256": dict(B=1, N=1024, D=256, direction="outgoing", mesh="1d", mask="ones"),
     "profile_n2048_d128": dict(B=1, N=2048, D=128, direction="outgoing", mesh="1d", mask="ones"),
     "profile_n2048_d256": dict(B=1, N=2048, D=256, direction="outgoing", mesh="1d", mask="ones"),
+    "profile_n1024_d512": dict(B=1, N=1024, D=512, direction="outgoing", mesh="1d", mask="ones"),
 }
 CPU_SAMPLE_N = 768  # token extent of the bounded CPU sample (same D, same distributions)
 E2E_MAX_BYTES = 24 << 30  # per-rank input size beyond which the pinned-host end-to-end leg is skipped

@@ -195,6 +195,10 @@ __device__ __forceinline__ void gate16_to_stage(const uint32_t (&gv)[16], const 
   }
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -499,6 +503,19 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             }
           }
           if (rb == 0) {  // the tensor core must have released the (single) operand tile before the first write
+            // That wait lasts most of a tile's MMA phase.  The rows of the three later batches are loaded only
+            // after it (no registers to park them in): ask L2 for them now, so that those loads are L2 hits.
+            if (!(kAblate & 2)) {
+#pragma unroll
+              for (int i = RB; i < ROWS_PER_WARP; ++i) {
+                const int w = tc.w0 + lw * ROWS_PER_WARP + i;
+                if (w < p.n_walk) {
+                  const uint8_t* row = xb + (row0 + static_cast<long>(w) * p.walk_rows) * D * 2;
+                  prefetch_l2(row + c0 * 16);
+                  if (has1) prefetch_l2(row + c1 * 16);
+                }
+              }
+            }
             ok = sm100::mbar_wait(&ctl->x_empty[0], buf_phase ^ 1, abort_flag, tmo);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
