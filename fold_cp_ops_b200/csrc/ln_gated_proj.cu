@@ -379,6 +379,7 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       constexpr uint32_t NB = C::kStBufs;
       constexpr uint32_t kLag = NB >= 2 ? NB - 2 : 0;   // bulk groups that may still read their buffer
       const int d_loc_n = p.d_loc;
+      const int sc = p.store_ch;   // channels one a|b store moves: the largest of 64 / 32 / 16 that divides D / cp
       uint32_t use = 0;
       bool ok = true, stamped = false;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -403,14 +404,14 @@ gated_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 stamped = true;
               }
 #pragma unroll 1
-              for (int k = 0; k < ((kAblate & 8) ? 0 : C::CH / 16); ++k) {
-                const int d = (c % C::kPerHalf) * C::CH + k * 16;  // first channel of the 16 inside the a (or b) half
+              for (int k = 0; k < ((kAblate & 8) ? 0 : C::CH / sc); ++k) {
+                const int d = (c % C::kPerHalf) * C::CH + k * sc;  // first channel of the group inside the a (or b) half
                 const int owner = d / d_loc_n;
                 const CUtensorMap* map = &om.ab[owner];
                 const int plane = h * d_loc_n + (d - owner * d_loc_n);
-                // sixteen channel rows of each token half: (64 tokens, 16 channels) boxes, 128-byte rows
-                sm100::tma_store_4d(map, src + k * 16 * 128, dst_x, dst_y, tc.b, plane);
-                sm100::tma_store_4d(map, src + C::kHalfBytes + k * 16 * 128, dst_x + kHalfTokens, dst_y, tc.b, plane);
+                // `sc` channel rows of each token half: (64 tokens, sc channels) boxes, 128-byte rows
+                sm100::tma_store_4d(map, src + k * sc * 128, dst_x, dst_y, tc.b, plane);
+                sm100::tma_store_4d(map, src + C::kHalfBytes + k * sc * 128, dst_x + kHalfTokens, dst_y, tc.b, plane);
               }
             } else {
               const int cw = p.gate_walk_dim == 1 ? tc.w0 : tc.line;

@@ -286,6 +286,7 @@ int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning
     a.ab.ptr[s] = ab_peers[s];
   }
   a.d_loc = d.d_loc;
+  a.store_ch = (d.d_loc % 64 == 0) ? 64 : ((d.d_loc % 32 == 0) ? 32 : 16);
   a.plane_elems = plan.plane_elems;
   a.gate_out = gate_out;
   if (static_cast<long>(geom->n) * geom->n > 0x7fffffffL)
@@ -294,7 +295,7 @@ int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning
   {
     // Store maps.  a|b: every owner's operand buffer as (x, y, batch, 2*D_loc planes); x is clipped
     // at the end of this rank's walk so a ragged tile cannot reach a neighbour's tokens.  Boxes are
-    // 64 tokens x 16 channel planes with the 128-byte swizzle (the layout stmatrix fills).
+    // 64 tokens x store_ch channel planes with the 128-byte swizzle (the layout stmatrix fills).
     const uint64_t n = static_cast<uint64_t>(geom->n);
     const bool flat = plan.dst_line == 0;  // whole block contiguous: one line, x runs over the plane
     a.dst_x0 = static_cast<int>(flat ? plan.dst_base : plan.dst_base % plan.dst_line);
@@ -302,7 +303,7 @@ int build_front(const trimul_geom_t* geom, const Derived& d, const trimul_tuning
     const uint64_t dims[4] = {static_cast<uint64_t>(a.dst_x0) + static_cast<uint64_t>(plan.n_walk), flat ? 1 : n,
                               static_cast<uint64_t>(geom->batch), static_cast<uint64_t>(2 * d.d_loc)};
     const uint64_t strides[3] = {flat ? n * n * 2 : n * 2, n * n * 2, n * n * 2 * geom->batch};
-    const uint32_t box[4] = {64, 1, 1, 16};
+    const uint32_t box[4] = {64, 1, 1, static_cast<uint32_t>(a.store_ch)};
     for (int s = 0; s < d.cp; ++s) {
       int rc = make_tmap(&out->maps.ab[s], ab_peers[s], 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != TRIMUL_OK) return rc;

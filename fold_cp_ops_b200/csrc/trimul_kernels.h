@@ -36,6 +36,7 @@ struct GatedProjArgs {
   // (2, D_loc, B, plane_rows, plane_cols); this rank fills [dst_base + line*dst_line + w]
   PeerPtrs ab;
   int d_loc;             // D / cp: channels of a (and of b) each rank contracts
+  int store_ch;          // channels per a|b store box (64, 32 or 16; divides d_loc, so a box has one owner)
   long plane_elems;      // plane_rows * plane_cols of the destination plane (global N*N)
   long dst_base;         // element offset of (line 0, w 0) inside a plane
   long dst_line;         // element stride between lines inside a plane
@@ -49,7 +50,7 @@ struct GatedProjArgs {
 };
 
 // Store-side tensor maps of the projection kernel.  ab[s]: rank s's operand buffer as
-// (x, y, batch, 2*D_loc planes), box 64 tokens x 16 planes, 128-byte swizzle; dim 0 is clipped at the end of
+// (x, y, batch, 2*D_loc planes), box 64 tokens x store_ch planes, 128-byte swizzle; dim 0 is clipped at the end of
 // this rank's walk so ragged tiles never touch a neighbour's tokens.  gate: the local gate buffer
 // as (D, walk | line, line | walk, batch), box 64 channels x 128 tokens, 128-byte swizzle.
 struct GatedOutMaps {
