@@ -117,6 +117,59 @@ def trimul_eager_module(x, direction, mask=None, *, eps=1e-5, **w) -> torch.Tens
     return F.linear(trin, _f(w["p_out_w"]), _f(w.get("p_out_b"))) * torch.sigmoid(F.linear(xn, _f(w["g_out_w"]), _f(w.get("g_out_b"))))
 
 
+def trimul_oracle_tiled(x, direction, mask=None, *, row_tile: int = 512, on_tile=None, eps=1e-5, **w):
+    """The oracle evaluated one ``(row_tile x row_tile)`` block of the OUTPUT grid at a time, the contraction
+    index kept whole -- the job of the reference's ``trimul_ref_chunked``
+    (``fold_cp_ops/workflows/trimul_autotune.py:1727-1815``): peak memory is O(row_tile * N * D) instead of
+    O(N^2 * D), so a large-N output can be checked without ever holding the fp32 oracle.
+
+    Without ``on_tile`` the blocks are assembled and returned (equal to :func:`trimul_oracle` up to fp32
+    summation order).  With ``on_tile(i0, i1, j0, j1, block)`` every fp32 block ``(B, i1-i0, j1-j0, D)`` is
+    handed to the callback instead and ``None`` is returned.  ``row_tile`` need not divide N."""
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"direction must be 'outgoing' or 'incoming'; got {direction!r}")
+    B, N, _, D = x.shape
+    T = int(row_tile) if row_tile and int(row_tile) > 0 else N
+    outgoing = direction == "outgoing"
+
+    def half(lo, hi, which):
+        # gated projection of the input lines [lo, hi) (rows for outgoing, columns for incoming), a or b half
+        xs = x[:, lo:hi] if outgoing else x[:, :, lo:hi]
+        xn = layer_norm(xs, w["norm_in_w"], w.get("norm_in_b"), eps)
+        p = xn @ w["p_in_w"].float().T
+        g = xn @ w["g_in_w"].float().T
+        if w.get("p_in_b") is not None:
+            p = p + w["p_in_b"].float()
+        if w.get("g_in_b") is not None:
+            g = g + w["g_in_b"].float()
+        ab = p * torch.sigmoid(g)
+        if mask is not None:
+            ms = mask[:, lo:hi] if outgoing else mask[:, :, lo:hi]
+            ab = ab * ms.float().unsqueeze(-1)
+        return ab[..., :D] if which == 0 else ab[..., D:]
+
+    out = None if on_tile is not None else torch.empty((B, N, N, D), dtype=torch.float32, device=x.device)
+    for i0 in range(0, N, T):
+        i1 = min(i0 + T, N)
+        a = half(i0, i1, 0)
+        for j0 in range(0, N, T):
+            j1 = min(j0 + T, N)
+            b = half(j0, j1, 1)
+            tri = torch.einsum("bikd,bjkd->bijd" if outgoing else "bkid,bkjd->bijd", a, b)
+            p_out = layer_norm(tri, w["norm_out_w"], w.get("norm_out_b"), eps) @ w["p_out_w"].float().T
+            if w.get("p_out_b") is not None:
+                p_out = p_out + w["p_out_b"].float()
+            g_out = layer_norm(x[:, i0:i1, j0:j1], w["norm_in_w"], w.get("norm_in_b"), eps) @ w["g_out_w"].float().T
+            if w.get("g_out_b") is not None:
+                g_out = g_out + w["g_out_b"].float()
+            block = p_out * torch.sigmoid(g_out)
+            if on_tile is not None:
+                on_tile(i0, i1, j0, j1, block)
+            else:
+                out[:, i0:i1, j0:j1] = block
+    return out
+
+
 def trimul_oracle(x, direction, mask=None, *, eps=1e-5, **w) -> torch.Tensor:
     """``(B, N, N, D)`` fp32 TriMul forward; keyword weights as in the reference's 12-key dict."""
     return trimul_stages(x, direction, mask, eps=eps, **w)["out"]

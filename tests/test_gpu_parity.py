@@ -98,6 +98,27 @@ def test_single_gpu_config_shape_against_gpu_evaluated_oracle(direction):
     _assert_parity(_run(case, direction), ref, f"config1 {direction}")
 
 
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_larger_shape_against_the_streamed_tiled_oracle(direction):
+    """N=768, D=256: the fp32 oracle is never materialised -- the tiled oracle (the reference's
+    ``trimul_ref_chunked`` form) runs on the GPU in fp32 (TF32 off) and every block is compared as it is made."""
+    from oracle.trimul_oracle import trimul_oracle_tiled
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    case = bf16_round_case(make_case(1, 768, 256, seed=41, bias="all", mask="pad"))
+    got = _run(case, direction).to(DEV)
+    cg = {k: (None if v is None else v.to(DEV)) for k, v in case.items()}
+    bad = [0, 0.0]
+
+    def on_tile(i0, i1, j0, j1, ref):
+        err = (got[:, i0:i1, j0:j1] - ref).abs()
+        bad[0] += int((err > 2e-2 + 6e-2 * ref.abs()).sum()) + int((err > 0.01 * ref.abs().max() + 0.01 * ref.abs()).sum())
+        bad[1] = max(bad[1], err.max().item())
+
+    trimul_oracle_tiled(cg["x"], direction, cg["mask"], row_tile=256, on_tile=on_tile, **{k: cg[k] for k in weights_of(case)})
+    assert bad[0] == 0, f"{bad[0]} elements beyond the bounds, max|err| = {bad[1]:.4f}"
+
+
 def test_off_centre_rows():
     """Rows whose mean is far from zero (|mean| >> std) must not lose the LayerNorm signal
     (the reference pins this for its own chains: tests/workflows/test_trimul_autotune.py:611-633)."""

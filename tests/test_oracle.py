@@ -53,13 +53,15 @@ _LIVE_SNIPPET = """
 import sys, numpy as np, torch
 sys.dont_write_bytecode = True
 sys.path.insert(0, {repo!r}); sys.path.insert(0, {ref!r})   # the reference's own package wins the name
-from fold_cp_ops.workflows.trimul_autotune import trimul_ref
+from fold_cp_ops.workflows.trimul_autotune import trimul_ref, trimul_ref_chunked
 from oracle.trimul_oracle import bf16_round_case, make_case, weights_of
 out = {{}}
 for direction in ("outgoing", "incoming"):
     for bias, mask in (("none", "none"), ("all", "random"), ("out", "pad")):
         case = bf16_round_case(make_case(B=2, N=24, D=128, seed=7, bias=bias, mask=mask))
         out[f"{{direction}}_{{bias}}_{{mask}}"] = trimul_ref(case["x"], direction, case["mask"], **weights_of(case), eps=1e-5).numpy()
+    case = bf16_round_case(make_case(B=1, N=40, D=128, seed=9, bias="all", mask="random"))
+    out[f"chunked_{{direction}}"] = trimul_ref_chunked(case["x"], direction, case["mask"], **weights_of(case), eps=1e-5, row_tile=16).numpy()
 np.savez({dst!r}, **out)
 """
 
@@ -87,6 +89,16 @@ def test_oracle_matches_live_reference(direction, bias, mask, live_reference):
     case = bf16_round_case(make_case(B=2, N=24, D=128, seed=7, bias=bias, mask=mask))
     ref = torch.from_numpy(live_reference[f"{direction}_{bias}_{mask}"])
     got = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    assert (got - ref).abs().max().item() <= 2e-5 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_tiled_oracle_matches_live_reference_chunked(direction, live_reference):
+    from oracle.trimul_oracle import trimul_oracle_tiled
+
+    case = bf16_round_case(make_case(B=1, N=40, D=128, seed=9, bias="all", mask="random"))
+    ref = torch.from_numpy(live_reference[f"chunked_{direction}"])
+    got = trimul_oracle_tiled(case["x"], direction, case["mask"], row_tile=16, eps=1e-5, **weights_of(case))
     assert (got - ref).abs().max().item() <= 2e-5 * max(1.0, ref.abs().max().item())
 
 
@@ -139,3 +151,24 @@ def test_eager_module_spelling_equals_the_restatement(direction):
     assert (a - b).abs().max().item() <= 2e-4 * max(1.0, a.abs().max().item())
     nomask = trimul_eager_module(case["x"], direction, None, **weights_of(case))
     assert torch.allclose(nomask, trimul_oracle(case["x"], direction, None, **weights_of(case)), atol=2e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_tiled_oracle_equals_the_full_oracle(direction):
+    """The memory-frugal form (output grid in blocks, contraction whole; the reference's ``trimul_ref_chunked``)
+    is the same function, with a block size that does not divide N, and streams the same blocks."""
+    from oracle.trimul_oracle import make_case, trimul_oracle, trimul_oracle_tiled, weights_of
+
+    case = make_case(2, 40, 128, seed=33, bias="all", mask="random")
+    full = trimul_oracle(case["x"], direction, case["mask"], **weights_of(case))
+    tiled = trimul_oracle_tiled(case["x"], direction, case["mask"], row_tile=16, **weights_of(case))
+    assert (tiled - full).abs().max().item() <= 2e-5 * max(1.0, full.abs().max().item())
+    seen = torch.zeros(40, 40, dtype=torch.int32)
+    worst = [0.0]
+
+    def on_tile(i0, i1, j0, j1, block):
+        seen[i0:i1, j0:j1] += 1
+        worst[0] = max(worst[0], (block - full[:, i0:i1, j0:j1]).abs().max().item())
+
+    assert trimul_oracle_tiled(case["x"], direction, case["mask"], row_tile=16, on_tile=on_tile, **weights_of(case)) is None
+    assert bool((seen == 1).all()) and worst[0] <= 2e-5 * max(1.0, full.abs().max().item())
