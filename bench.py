@@ -348,8 +348,13 @@ def run_ours(args):
     torch.manual_seed(0)
     w = make_layer_weights(D, 0, dev)
     layer = trimul_module_from_weights(w)
+    tuning = None
+    if args.contract_form is not None:
+        from fold_cp_ops_b200.distributed.workflows.trimul_tuning import BackTuning, TriMulTuning
+
+        tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form))
     trimul = TriangularMultiplication(layer, direction, mesh if cp > 1 else None, dm, placements=placements if cp > 1 else None,
-                                      dtype=torch.bfloat16)
+                                      dtype=torch.bfloat16, tuning=tuning)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     x_bytes = B * ni * nj * D * 2
     do_e2e = not args.kernels_only and not args.no_e2e and x_bytes <= E2E_MAX_BYTES
@@ -592,7 +597,8 @@ def run_ours(args):
             "config": {"workload": args.workload, "B": B, "N": N, "D": D, "direction": direction,
                        "parallelism": f"cp{cp}" if not two_d else f"cp{cp0}x{cp1}",
                        "mesh": "2-D, rows x columns sharded" if two_d else "1-D, rows sharded", "mask": wl["mask"],
-                       "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed"},
+                       "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed",
+                       "contract_form": args.contract_form or "engine default"},
             "clocks": clocks,
             "e2e": e2e if e2e is not None else {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
                                                 "d2h_bytes_per_step": bytes_out,
@@ -689,6 +695,8 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input forward only (skip the e2e, CPU-baseline and verify legs); for profilers")
     ap.add_argument("--no-e2e", action="store_true", help="skip the pinned-host end-to-end leg")
+    ap.add_argument("--contract-form", choices=("pair", "single"), default=None,
+                    help="force the contraction kernel's form (default: the engine's choice, CTA pairs when the shape allows)")
     ap.add_argument("--stage-times", action="store_true",
                     help="with --kernels-only: still report the per-kernel times (used with profiling builds of the "
                          "library selected by CPO_TRIMUL_LIB, whose results are wrong by construction)")
