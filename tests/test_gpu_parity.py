@@ -218,6 +218,67 @@ def test_kernel_ln_gated_proj(direction, D, N, B):
     assert (err <= 0.01).all(), err.max().item()
 
 
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("D,cp0,cp1,N,B", [
+    (128, 8, 1, 64, 1),    # 16 channels per rank: the smallest store box
+    (256, 8, 1, 64, 2),    # the eight-rank split of the headline width: 32 channels per rank
+    (384, 8, 1, 64, 1),    # 48 channels per rank: owner boundaries fall inside a 64-channel group
+    (512, 8, 1, 128, 1),   # 64 channels per rank, wide-row kernels
+    (256, 2, 4, 64, 1),    # 2-D grid, rows x columns
+    (128, 4, 2, 64, 2),
+    (384, 2, 2, 48, 1),
+    (256, 4, 1, 96, 1),
+    (256, 2, 1, 48, 2),
+])
+def test_every_rank_of_a_cp_grid_run_in_turn_on_one_gpu(direction, D, cp0, cp1, N, B):
+    """The cp > 1 data path without a second GPU: every rank's kernels are launched one after the other
+    on this GPU through the stateless entry points, with the peers' receive buffers being plain local
+    allocations.  No kernel waits on another (all projections finish before the first contraction
+    starts, all contractions before the first output kernel), so this covers the owner arithmetic and
+    the store boxes of both fused reshards for every rank of the grid -- eight ranks included -- and
+    is compared with the fp32 oracle on the global tensor."""
+    from fold_cp_ops_b200 import kernels as K
+
+    cp = cp0 * cp1
+    case = bf16_round_case(make_case(B, N, D, seed=D + 10 * cp0 + cp1, bias="all", mask="random"))
+    eng = _engine(case)
+    W = eng.weights
+    x = case["x"].to(DEV).bfloat16()
+    mask = case["mask"].to(DEV)
+    ni, nj = N // cp0, N // cp1
+    geoms = [K.make_geom(B, N, D, direction, 1e-5, cp0, cp1, r) for r in range(cp)]
+    ws = K.workspace_bytes(geoms[0])
+    nan16 = lambda nbytes: torch.full((nbytes // 2,), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ab = [nan16(ws.ab_bytes) for _ in range(cp)]
+    tri = [nan16(ws.tri_bytes) for _ in range(cp)]
+    gate = [nan16(ws.gate_bytes) for _ in range(cp)]
+    block = lambda t, r: t[:, (r // cp1) * ni:(r // cp1 + 1) * ni, (r % cp1) * nj:(r % cp1 + 1) * nj].contiguous()
+    for r, g in enumerate(geoms):
+        K.ln_gated_proj(g, block(x, r), block(mask, r), W.norm_in_w, W.norm_in_b, W.w_packed, W.bias_packed,
+                        [t.data_ptr() for t in ab], gate[r], eng.status)
+    torch.cuda.synchronize()
+    eng.check()
+    for r, g in enumerate(geoms):
+        assert not torch.isnan(ab[r]).any(), f"rank {r}: part of its a|b planes was never written"
+        K.tri_contract(g, ab[r], [t.data_ptr() for t in tri], eng.status)
+    torch.cuda.synchronize()
+    eng.check()
+    out = torch.full_like(x, float("nan"))
+    for r, g in enumerate(geoms):
+        assert not torch.isnan(tri[r]).any(), f"rank {r}: part of its contraction input was never written"
+        out_r = torch.full((B, ni, nj, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.ln_out_proj(g, tri[r], gate[r], W.w_fold, W.cd, out_r, eng.status)
+        out[:, (r // cp1) * ni:(r // cp1 + 1) * ni, (r % cp1) * nj:(r % cp1 + 1) * nj] = out_r
+    torch.cuda.synchronize()
+    eng.check()
+    ref = trimul_oracle(case["x"], direction, case["mask"], eps=1e-5, **weights_of(case))
+    _assert_parity(out.float().cpu(), ref, f"cp{cp0}x{cp1} D={D} {direction}")
+    one = eng.forward(x, direction, mask)
+    torch.cuda.synchronize()
+    # the same arithmetic per element as the one-rank forward (only the partition differs)
+    assert (out.float() - one.float()).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
 @pytest.mark.parametrize("N,planes_d", [(8, 128), (64, 128), (200, 128), (1024, 128)])
 def test_kernel_tri_contract(N, planes_d):
     from fold_cp_ops_b200 import kernels as K
