@@ -293,3 +293,56 @@ def test_slurm_first_host():
     assert DM._slurm_first_host("gpu7,gpu8") == "gpu7"
     assert DM._slurm_first_host("dgx[1,2]") == "dgx1"
     assert DM._slurm_first_host("") is None
+
+
+# ------------------------------------------------------------------------------------------------
+def _spot_check_ranks_1d(rank, world):
+    return _spot_check_ranks(rank, world, two_d=False)
+
+
+def _spot_check_ranks_2d(rank, world):
+    return _spot_check_ranks(rank, world, two_d=True)
+
+
+def _spot_check_ranks(rank, world, two_d):
+    """bench.py's full-size parity check on `world` CPU ranks: every rank holds its block of a small global
+    tensor and of the full oracle's output; the patch oracle, fed by the line gather, must agree on every
+    rank, and a corrupted block on ONE rank must fail the line for everybody."""
+    import torch.distributed as dist
+
+    import bench
+    from oracle.trimul_oracle import trimul_oracle
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cp0, cp1 = (2, world // 2) if two_d else (world, 1)
+        r0, r1 = (rank // cp1, rank % cp1) if two_d else (rank, 0)
+        wl = dict(B=1, N=24 * max(cp0, cp1), D=128, mask="pad")
+        B, N, D = wl["B"], wl["N"], wl["D"]
+        dev = torch.device("cpu")
+        w = bench.make_layer_weights(D, 0, dev)
+        x = torch.randn(B, N, N, D, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+        tm = bench.token_mask(wl["mask"], N)
+        mask = (tm[:, None] * tm[None, :]).expand(B, -1, -1)
+        ni, nj = N // cp0, N // cp1
+        blk = lambda t: t[:, r0 * ni:(r0 + 1) * ni, r1 * nj:(r1 + 1) * nj].contiguous()
+        results = {}
+        for direction in ("outgoing", "incoming"):
+            full = trimul_oracle(x.float(), direction, mask, **{k: (None if v is None else v.float()) for k, v in w.items()})
+            good = bench.spot_check(w, blk(x), blk(full), wl, direction, world, cp0, cp1, rank, r0, r1, dev, rows=2, cols=16)
+            assert good["within_bound_on_every_rank"] and good["max_abs_err"] < 1e-3 and good["ranks_checked"] == world, good
+            wrong = blk(full).clone()
+            if rank == world - 1:
+                wrong += 1.0
+            bad = bench.spot_check(w, blk(x), wrong, wl, direction, world, cp0, cp1, rank, r0, r1, dev, rows=2, cols=16)
+            assert not bad["within_bound_on_every_rank"], bad
+            results[direction] = good["max_abs_err"]
+        return results
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,grid", [(2, "1d"), (4, "2d"), (8, "1d"), (8, "2d")])
+def test_bench_spot_check_gathers_lines_across_ranks(world, grid):
+    """Rows over 2 and 8 ranks and the 2-D grids (2,2) and (2,4): the grids `bench.py --gpus N` runs."""
+    _run(f"_spot_check_ranks_{grid}", world=world, timeout=300)
