@@ -77,7 +77,11 @@ def measured_peaks():
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-KB_DRAM_BYTES_PER_PLANE_ELEMENT = 6.038
+#: DRAM bytes (read + write) the contraction kernel moves per channel plane, from one-pass ncu captures of whole
+#: launches (profiles/tri_contract_kernel_n1024_d256.md, profiles/tri_contract_kernel_n4096_d256.md).  Planes are
+#: independent, so a launch moves planes x this; it does NOT scale with N^2: first touch only at N=1024 (a plane
+#: pair is 4 MB), 3.9x first touch at N=4096 (a plane pair is 64 MB and the tile re-reads miss L2).
+KB_DRAM_BYTES_PER_PLANE = {1024: 1.6207e9 / 256, 4096: (58.84e9 + 8.59e9) / 256}
 
 
 class ClockSampler:
@@ -349,10 +353,10 @@ def run_ours(args):
     w = make_layer_weights(D, 0, dev)
     layer = trimul_module_from_weights(w)
     tuning = None
-    if args.contract_form is not None:
+    if args.contract_form is not None or args.contract_band is not None:
         from fold_cp_ops_b200.distributed.workflows.trimul_tuning import BackTuning, TriMulTuning
 
-        tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form))
+        tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form, band_rows=args.contract_band))
     trimul = TriangularMultiplication(layer, direction, mesh if cp > 1 else None, dm, placements=placements if cp > 1 else None,
                                       dtype=torch.bfloat16, tuning=tuning)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
@@ -534,16 +538,19 @@ def run_ours(args):
         tf = fl / (ms * 1e-3) / 1e12
         # dominant kernel: the contraction; algorithmic FLOPs per launch = 2*B*(D/cp)*N^3 on each rank
         fl_b = 2.0 * B * (D / cp) * N ** 3
+        # one launch contracts planes_b batch planes of this rank's D/cp channels (planes_b = B unless the
+        # workspace was capped to one batch plane per launch)
+        planes_b = getattr(next(iter(eng._ws.values())), "planes_b", B) if eng is not None and eng._ws else B
+        planes_per_launch = planes_b * (D // cp)
         ach = fl_b / (t_b * 1e-3) / 1e12 if t_b > 0 else None
         peak = peaks["bf16_tflops_sustained"]
         roof = {"bound": "tensor", "kernel": "tri_contract_pair_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": (ach / peak) if ach else None,
-                # DRAM bytes per launch: ncu measured 6.038 B per plane element (read 4.113 + write 1.925) on
-                # profile_n1024_d256 (profiles/tri_contract_kernel_n1024_d256.md); first-touch traffic only, so it
-                # scales with planes * N^2
-                "traffic": KB_DRAM_BYTES_PER_PLANE_ELEMENT * B * (D / cp) * N * N,
-                "traffic_unit": "bytes per launch (ncu capture at N=1024 scaled by planes*N^2; the proportionality "
-                                "is assumed, not captured, at larger N)",
+                "traffic": (KB_DRAM_BYTES_PER_PLANE[N] * planes_per_launch) if N in KB_DRAM_BYTES_PER_PLANE else None,
+                "traffic_unit": "DRAM bytes per launch: one-pass ncu capture of a whole launch at this N, times the "
+                                "planes of one launch / the captured 256 (planes are independent); null where this N "
+                                "was not captured",
+                "traffic_first_touch": 6.0 * planes_per_launch * N * N,
                 "peak_source": f"{peaks['source']} (sustained: the kernel runs inside a long step)",
                 "frac_of_burst_peak": (ach / peaks["bf16_tflops"]) if ach else None,
                 "stage_ms": {"ln_gated_proj": t_a, "tri_contract": t_b, "ln_out_proj": t_c},
@@ -598,7 +605,8 @@ def run_ours(args):
                        "parallelism": f"cp{cp}" if not two_d else f"cp{cp0}x{cp1}",
                        "mesh": "2-D, rows x columns sharded" if two_d else "1-D, rows sharded", "mask": wl["mask"],
                        "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed",
-                       "contract_form": args.contract_form or "engine default"},
+                       "contract_form": args.contract_form or "engine default",
+                       "contract_band_rows": args.contract_band if args.contract_band is not None else "engine default"},
             "clocks": clocks,
             "e2e": e2e if e2e is not None else {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
                                                 "d2h_bytes_per_step": bytes_out,
@@ -695,6 +703,8 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input forward only (skip the e2e, CPU-baseline and verify legs); for profilers")
     ap.add_argument("--no-e2e", action="store_true", help="skip the pinned-host end-to-end leg")
+    ap.add_argument("--contract-band", type=int, default=None,
+                    help="tile rows per band of the contraction kernel's tile walk (1 = row-major; default: the engine's choice)")
     ap.add_argument("--contract-form", choices=("pair", "single"), default=None,
                     help="force the contraction kernel's form (default: the engine's choice, CTA pairs when the shape allows)")
     ap.add_argument("--stage-times", action="store_true",

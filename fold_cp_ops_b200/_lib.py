@@ -60,7 +60,8 @@ class Geom(C.Structure):
 
 
 class Tuning(C.Structure):
-    _fields_ = [("contract_form", C.c_int32), ("front_fixed_order", C.c_int32), ("reserved", C.c_int32 * 6)]
+    _fields_ = [("contract_form", C.c_int32), ("front_fixed_order", C.c_int32),
+                ("contract_band_rows", C.c_int32), ("reserved", C.c_int32 * 5)]
 
 
 CONTRACT_DEFAULT, CONTRACT_SINGLE, CONTRACT_PAIR = 0, 1, 2

@@ -96,8 +96,8 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         const int plane = static_cast<int>(t / tiles_per_plane);
         const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
-        const int ti = r / tiles_j;
-        const int tj = r - ti * tiles_j;
+        int ti, tj;
+        tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
         bool ok = true;
         for (int kc = 0; kc < num_k; ++kc) {
           if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
@@ -163,8 +163,8 @@ tri_contract_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int plane = static_cast<int>(t / tiles_per_plane);
       const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
-      const int ti = r / tiles_j;
-      const int tj = r - ti * tiles_j;
+      int ti, tj;
+      tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);  // the warp leaves together: tcgen05.ld is warp-collective
       if (!ok) {

@@ -98,8 +98,8 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (long t = pair; t < total_tiles; t += num_pairs) {
         const int plane = static_cast<int>(t / tiles_per_plane);
         const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
-        const int ti = r / tiles_j;
-        const int tj = r - ti * tiles_j;
+        int ti, tj;
+        tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
         bool ok = true;
         for (int kc = 0; kc < num_k; ++kc) {
           if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
@@ -165,8 +165,8 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (long t = pair; t < total_tiles; t += num_pairs) {
       const int plane = static_cast<int>(t / tiles_per_plane);
       const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
-      const int ti = r / tiles_j;
-      const int tj = r - ti * tiles_j;
+      int ti, tj;
+      tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

@@ -58,6 +58,19 @@ __device__ __forceinline__ void timeline_max(unsigned long long* tl, int slot) {
   if (tl != nullptr) atomicMax(tl + slot, static_cast<unsigned long long>(sm100::globaltimer_ns()));
 }
 
+// Order in which the contraction kernels walk the output tiles of one plane.  The plane's tile grid is cut
+// into bands of `band_rows` tile rows; inside a band the walk is column by column.  The CTAs of one wave hold
+// consecutive tiles, so a wave covers about band_rows x (wave / band_rows) tiles and streams that many A row
+// strips and B row strips through L2 instead of a few A strips and ALL B strips (band_rows = 1, row-major).
+__device__ __forceinline__ void tile_of(int r, int tiles_i, int tiles_j, int band_rows, int& ti, int& tj) {
+  const int band_tiles = band_rows * tiles_j;
+  const int band = r / band_tiles;
+  const int rem = r - band * band_tiles;
+  const int rows = min(band_rows, tiles_i - band * band_rows);
+  tj = rem / rows;
+  ti = band * band_rows + (rem - tj * rows);
+}
+
 // Base pointers of one logical buffer on every rank of the cp group (index = flat cp rank).
 // At cp=1 only ptr[0] is used and it is local memory.
 struct PeerPtrs {

@@ -74,6 +74,7 @@ struct TriContractArgs {
   PeerPtrs out;
   int ni_loc, nj_loc, cp1;
   int chan_offset;
+  int band_rows;    // tile rows per band of the tile walk (>= 1; 1 = row-major)
   unsigned long long* timeline;  // optional device timeline, nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;

@@ -64,6 +64,7 @@ class BackTuning:
     pingpong: Optional[bool] = _knob("back_pingpong")
     cluster_n: Optional[int] = _knob("back_cluster_n")
     contract_form: Optional[str] = _knob("contract_form")
+    band_rows: Optional[int] = _knob("contract_band_rows")
 
 
 @_tuning_group

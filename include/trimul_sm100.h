@@ -90,7 +90,10 @@ typedef struct trimul_tuning {
   int32_t front_fixed_order; /* 1: every CTA of the projection kernel walks the gated chunks in the same
                                 order; 0: CTAs start at different chunks so that, at cp > 1, the grid's
                                 stores reach all owner ranks at any moment */
-  int32_t reserved[6];
+  int32_t contract_band_rows; /* tile rows per band of the contraction kernel's tile walk: inside a band
+                                 the walk is column by column, so one wave of CTAs streams about as many A
+                                 row strips as B row strips through L2.  0: the library's choice; 1: row-major */
+  int32_t reserved[5];
 } trimul_tuning_t;
 
 /* Optional device timeline of one forward: TRIMUL_TIMELINE_SLOTS x uint64 of %globaltimer (ns) on this

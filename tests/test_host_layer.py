@@ -198,6 +198,11 @@ def test_tuning_surface():
     real = TriMulTuning(back=BackTuning(contract_form="single"), front=FrontTuning(fixed_order=True),
                         transport=TransportTuning(wait_timeout_ms=500.0))
     assert real.to_engine_kwargs() == {"front_fixed_order": True, "contract_form": "single", "wait_timeout_ms": 500.0}
+    assert TriMulTuning(back=BackTuning(band_rows=4)).to_engine_kwargs() == {"contract_band_rows": 4}
+    from fold_cp_ops_b200 import kernels as K
+    assert K.make_tuning("pair", contract_band_rows=4).contract_band_rows == 4 and K.make_tuning().contract_band_rows == 0
+    with pytest.raises(ValueError, match="contract_band_rows"):
+        K.make_tuning(contract_band_rows=-1)
     with pytest.raises(TypeError, match="tile_mm"):
         FrontTuning(tile_mm=(128, 128))
     with pytest.raises(Exception):
