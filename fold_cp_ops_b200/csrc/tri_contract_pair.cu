@@ -63,6 +63,8 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int tiles_per_plane = tiles_i * tiles_j;
   const long total_tiles = static_cast<long>(tiles_per_plane) * p.planes;
   const int num_k = (p.n_k + BK - 1) / BK;
+  const int rot_i = (p.rot_rows / (2 * BM)) % tiles_i;   // first tile row / column of this rank's own block
+  const int rot_j = (p.rot_cols / BN) % tiles_j;
 
   if (threadIdx.x == 0) {
     timeline_min(p.timeline, kTlContractStart);
@@ -99,7 +101,7 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int plane = static_cast<int>(t / tiles_per_plane);
         const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
         int ti, tj;
-        tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
+        tile_of(r, tiles_i, tiles_j, p.band_rows, rot_i, rot_j, ti, tj);
         bool ok = true;
         for (int kc = 0; kc < num_k; ++kc) {
           if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
@@ -166,7 +168,7 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int plane = static_cast<int>(t / tiles_per_plane);
       const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
       int ti, tj;
-      tile_of(r, tiles_i, tiles_j, p.band_rows, ti, tj);
+      tile_of(r, tiles_i, tiles_j, p.band_rows, rot_i, rot_j, ti, tj);
       bool ok = sm100::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, tmo);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

@@ -390,6 +390,10 @@ int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tun
   const int band = tuning != nullptr ? tuning->contract_band_rows : 0;
   if (band < 0) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_band_rows=%d must be >= 0", band);
   a.band_rows = band > 0 ? band : kDefaultBandRows;
+  // every rank starts its walk at the block of the result it owns itself and all ranks advance alike, so at any
+  // moment the ranks' stores go to different owners (a rotation of the ranks) instead of all to the same one
+  a.rot_rows = static_cast<int>(d.i_off);
+  a.rot_cols = static_cast<int>(d.j_off);
   memset(&out->maps, 0, sizeof(out->maps));
   {
     // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)

@@ -62,13 +62,20 @@ __device__ __forceinline__ void timeline_max(unsigned long long* tl, int slot) {
 // into bands of `band_rows` tile rows; inside a band the walk is column by column.  The CTAs of one wave hold
 // consecutive tiles, so a wave covers about band_rows x (wave / band_rows) tiles and streams that many A row
 // strips and B row strips through L2 instead of a few A strips and ALL B strips (band_rows = 1, row-major).
-__device__ __forceinline__ void tile_of(int r, int tiles_i, int tiles_j, int band_rows, int& ti, int& tj) {
+// `rot_i` / `rot_j` shift where the walk starts (in tiles, modulo the grid): at cp > 1 every rank starts at the
+// tiles whose result it owns itself, so that at any moment the ranks' stores go to different owners instead of
+// all to the owner of the first rows.
+__device__ __forceinline__ void tile_of(int r, int tiles_i, int tiles_j, int band_rows, int rot_i, int rot_j, int& ti,
+                                        int& tj) {
   const int band_tiles = band_rows * tiles_j;
   const int band = r / band_tiles;
   const int rem = r - band * band_tiles;
   const int rows = min(band_rows, tiles_i - band * band_rows);
   tj = rem / rows;
-  ti = band * band_rows + (rem - tj * rows);
+  ti = band * band_rows + (rem - tj * rows) + rot_i;
+  tj += rot_j;
+  if (ti >= tiles_i) ti -= tiles_i;
+  if (tj >= tiles_j) tj -= tiles_j;
 }
 
 // Base pointers of one logical buffer on every rank of the cp group (index = flat cp rank).

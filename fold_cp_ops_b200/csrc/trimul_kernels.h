@@ -75,6 +75,7 @@ struct TriContractArgs {
   int ni_loc, nj_loc, cp1;
   int chan_offset;
   int band_rows;    // tile rows per band of the tile walk (>= 1; 1 = row-major)
+  int rot_rows, rot_cols;  // the walk starts at the tile holding this result row / column (this rank's own block)
   unsigned long long* timeline;  // optional device timeline, nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;

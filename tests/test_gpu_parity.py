@@ -237,6 +237,8 @@ def test_kernel_ln_gated_proj(direction, D, N, B):
     (384, 2, 2, 48, 1),
     (256, 4, 1, 96, 1),
     (256, 2, 1, 48, 2),
+    (128, 2, 1, 768, 1),   # several contraction tiles per plane: each rank's tile walk starts at its own block
+    (128, 2, 2, 768, 1),
 ])
 def test_every_rank_of_a_cp_grid_run_in_turn_on_one_gpu(direction, D, cp0, cp1, N, B):
     """The cp > 1 data path without a second GPU: every rank's kernels are launched one after the other
