@@ -353,10 +353,11 @@ def run_ours(args):
     w = make_layer_weights(D, 0, dev)
     layer = trimul_module_from_weights(w)
     tuning = None
-    if args.contract_form is not None or args.contract_band is not None:
+    if args.contract_form is not None or args.contract_band is not None or args.contract_fixed_start:
         from fold_cp_ops_b200.distributed.workflows.trimul_tuning import BackTuning, TriMulTuning
 
-        tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form, band_rows=args.contract_band))
+        tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form, band_rows=args.contract_band,
+                                                  fixed_start=True if args.contract_fixed_start else None))
     trimul = TriangularMultiplication(layer, direction, mesh if cp > 1 else None, dm, placements=placements if cp > 1 else None,
                                       dtype=torch.bfloat16, tuning=tuning)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
@@ -606,7 +607,8 @@ def run_ours(args):
                        "mesh": "2-D, rows x columns sharded" if two_d else "1-D, rows sharded", "mask": wl["mask"],
                        "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed",
                        "contract_form": args.contract_form or "engine default",
-                       "contract_band_rows": args.contract_band if args.contract_band is not None else "engine default"},
+                       "contract_band_rows": args.contract_band if args.contract_band is not None else "engine default",
+                       "contract_fixed_start": bool(args.contract_fixed_start)},
             "clocks": clocks,
             "e2e": e2e if e2e is not None else {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
                                                 "d2h_bytes_per_step": bytes_out,
@@ -703,6 +705,8 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input forward only (skip the e2e, CPU-baseline and verify legs); for profilers")
     ap.add_argument("--no-e2e", action="store_true", help="skip the pinned-host end-to-end leg")
+    ap.add_argument("--contract-fixed-start", action="store_true",
+                    help="every rank walks the contraction's tiles from tile (0, 0) instead of from its own block")
     ap.add_argument("--contract-band", type=int, default=None,
                     help="tile rows per band of the contraction kernel's tile walk (1 = row-major; default: the engine's choice)")
     ap.add_argument("--contract-form", choices=("pair", "single"), default=None,

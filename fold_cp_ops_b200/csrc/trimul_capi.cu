@@ -392,8 +392,9 @@ int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tun
   a.band_rows = band > 0 ? band : kDefaultBandRows;
   // every rank starts its walk at the block of the result it owns itself and all ranks advance alike, so at any
   // moment the ranks' stores go to different owners (a rotation of the ranks) instead of all to the same one
-  a.rot_rows = static_cast<int>(d.i_off);
-  a.rot_cols = static_cast<int>(d.j_off);
+  const bool fixed_start = tuning != nullptr && tuning->contract_fixed_start != 0;
+  a.rot_rows = fixed_start ? 0 : static_cast<int>(d.i_off);
+  a.rot_cols = fixed_start ? 0 : static_cast<int>(d.j_off);
   memset(&out->maps, 0, sizeof(out->maps));
   {
     // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)

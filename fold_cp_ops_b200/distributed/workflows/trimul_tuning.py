@@ -65,6 +65,7 @@ class BackTuning:
     cluster_n: Optional[int] = _knob("back_cluster_n")
     contract_form: Optional[str] = _knob("contract_form")
     band_rows: Optional[int] = _knob("contract_band_rows")
+    fixed_start: Optional[bool] = _knob("contract_fixed_start")
 
 
 @_tuning_group

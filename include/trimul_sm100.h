@@ -93,7 +93,10 @@ typedef struct trimul_tuning {
   int32_t contract_band_rows; /* tile rows per band of the contraction kernel's tile walk: inside a band
                                  the walk is column by column, so one wave of CTAs streams about as many A
                                  row strips as B row strips through L2.  0: the library's choice; 1: row-major */
-  int32_t reserved[5];
+  int32_t contract_fixed_start; /* 1: every rank walks the contraction's tiles from tile (0, 0); 0: each rank
+                                   starts at the block of the result it owns, so that at cp > 1 the ranks' stores
+                                   go to different owners at any moment */
+  int32_t reserved[4];
 } trimul_tuning_t;
 
 /* Optional device timeline of one forward: TRIMUL_TIMELINE_SLOTS x uint64 of %globaltimer (ns) on this

@@ -198,7 +198,8 @@ def test_tuning_surface():
     real = TriMulTuning(back=BackTuning(contract_form="single"), front=FrontTuning(fixed_order=True),
                         transport=TransportTuning(wait_timeout_ms=500.0))
     assert real.to_engine_kwargs() == {"front_fixed_order": True, "contract_form": "single", "wait_timeout_ms": 500.0}
-    assert TriMulTuning(back=BackTuning(band_rows=4)).to_engine_kwargs() == {"contract_band_rows": 4}
+    assert TriMulTuning(back=BackTuning(band_rows=4, fixed_start=True)).to_engine_kwargs() == {
+        "contract_band_rows": 4, "contract_fixed_start": True}
     from fold_cp_ops_b200 import kernels as K
     assert K.make_tuning("pair", contract_band_rows=4).contract_band_rows == 4 and K.make_tuning().contract_band_rows == 0
     with pytest.raises(ValueError, match="contract_band_rows"):
