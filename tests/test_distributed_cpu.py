@@ -317,7 +317,7 @@ def _spot_check_ranks(rank, world, two_d):
     try:
         cp0, cp1 = (2, world // 2) if two_d else (world, 1)
         r0, r1 = (rank // cp1, rank % cp1) if two_d else (rank, 0)
-        wl = dict(B=1, N=24 * max(cp0, cp1), D=128, mask="pad")
+        wl = dict(B=1, N=16 * max(cp0, cp1), D=128, mask="pad")
         B, N, D = wl["B"], wl["N"], wl["D"]
         dev = torch.device("cpu")
         w = bench.make_layer_weights(D, 0, dev)
