@@ -80,8 +80,8 @@ def measured_peaks():
 #: DRAM bytes (read + write) the contraction kernel moves per channel plane, from one-pass ncu captures of whole
 #: launches (profiles/tri_contract_kernel_n1024_d256.md, profiles/tri_contract_kernel_n4096_d256.md).  Planes are
 #: independent, so a launch moves planes x this; it does NOT scale with N^2: first touch only at N=1024 (a plane
-#: pair is 4 MB), 3.9x first touch at N=4096 (a plane pair is 64 MB and the tile re-reads miss L2).
-KB_DRAM_BYTES_PER_PLANE = {1024: 1.6207e9 / 256, 4096: (58.84e9 + 8.59e9) / 256}
+#: pair is 4 MB), 2.2x first touch at N=4096 (a plane pair is 64 MB and part of the tile re-reads miss L2).
+KB_DRAM_BYTES_PER_PLANE = {1024: 1.6207e9 / 256, 4096: (48.14e9 + 8.58e9) / 256}
 
 
 class ClockSampler:
@@ -353,11 +353,12 @@ def run_ours(args):
     w = make_layer_weights(D, 0, dev)
     layer = trimul_module_from_weights(w)
     tuning = None
-    if args.contract_form is not None or args.contract_band is not None or args.contract_fixed_start:
+    if args.contract_form is not None or args.contract_band is not None or args.contract_fixed_start or args.contract_pace is not None:
         from fold_cp_ops_b200.distributed.workflows.trimul_tuning import BackTuning, TriMulTuning
 
         tuning = TriMulTuning(back=BackTuning(contract_form=args.contract_form, band_rows=args.contract_band,
-                                                  fixed_start=True if args.contract_fixed_start else None))
+                                                  fixed_start=True if args.contract_fixed_start else None,
+                                                  pace_ns=args.contract_pace))
     trimul = TriangularMultiplication(layer, direction, mesh if cp > 1 else None, dm, placements=placements if cp > 1 else None,
                                       dtype=torch.bfloat16, tuning=tuning)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
@@ -608,7 +609,8 @@ def run_ours(args):
                        "l2": "inputs (>= 1 GB per rank) exceed the 126 MB L2; no flush needed",
                        "contract_form": args.contract_form or "engine default",
                        "contract_band_rows": args.contract_band if args.contract_band is not None else "engine default",
-                       "contract_fixed_start": bool(args.contract_fixed_start)},
+                       "contract_fixed_start": bool(args.contract_fixed_start),
+                       "contract_pace_ns": args.contract_pace if args.contract_pace is not None else "engine default"},
             "clocks": clocks,
             "e2e": e2e if e2e is not None else {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
                                                 "d2h_bytes_per_step": bytes_out,
@@ -705,6 +707,9 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input forward only (skip the e2e, CPU-baseline and verify legs); for profilers")
     ap.add_argument("--no-e2e", action="store_true", help="skip the pinned-host end-to-end leg")
+    ap.add_argument("--contract-pace", type=int, default=None,
+                    help="longest wait (ns) of a CTA pair of the contraction for the other pairs before a tile; "
+                         "0 = the library's choice, negative = off")
     ap.add_argument("--contract-fixed-start", action="store_true",
                     help="every rank walks the contraction's tiles from tile (0, 0) instead of from its own block")
     ap.add_argument("--contract-band", type=int, default=None,

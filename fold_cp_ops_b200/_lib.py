@@ -62,7 +62,7 @@ class Geom(C.Structure):
 class Tuning(C.Structure):
     _fields_ = [("contract_form", C.c_int32), ("front_fixed_order", C.c_int32),
                 ("contract_band_rows", C.c_int32), ("contract_fixed_start", C.c_int32),
-                ("reserved", C.c_int32 * 4)]
+                ("contract_pace_ns", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 CONTRACT_DEFAULT, CONTRACT_SINGLE, CONTRACT_PAIR = 0, 1, 2

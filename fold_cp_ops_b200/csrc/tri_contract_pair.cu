@@ -42,6 +42,15 @@ struct SmemCtl {
 
 constexpr int kSmemBytes = kStages * kStageBytes + tri::kOutStageBytes + 1024 /*align slack*/ + 256 /*ctl*/;
 
+// Wave pacing (a performance hint, never a dependency).  Tiles that run at the same time share operand
+// strips through L2 only while they move through K together; left alone, the pairs drift apart by a good
+// part of a tile and most of that sharing is lost.  Before loading its n-th tile a pair's first producer
+// counts itself in and waits -- for at most `pace_ns`, a time the six loaded stages cover -- until the other
+// pairs have started their n-th tile too.  A pair that is late never waits, an early pair gives up after
+// pace_ns and loads anyway, so no result and no termination depends on the counter; the last pair out resets
+// it.  [0]: tiles started, [1]: pairs finished.
+__device__ unsigned int g_wave_pace[2];
+
 }  // namespace
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -97,11 +106,20 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       sm100::tma_prefetch_desc(&tmA);
       sm100::tma_prefetch_desc(&tmB);
       PipeState ps{0, 0};
-      for (long t = pair; t < total_tiles; t += num_pairs) {
+      long wave_end = num_pairs;   // tiles that have started once every pair has started its current one
+      for (long t = pair; t < total_tiles; t += num_pairs, wave_end += num_pairs) {
         const int plane = static_cast<int>(t / tiles_per_plane);
         const int r = static_cast<int>(t - static_cast<long>(plane) * tiles_per_plane);
         int ti, tj;
         tile_of(r, tiles_i, tiles_j, p.band_rows, rot_i, rot_j, ti, tj);
+        if (p.pace_ns != 0 && cta == 0) {
+          const unsigned int target = static_cast<unsigned int>(wave_end < total_tiles ? wave_end : total_tiles);
+          atomicAdd(&g_wave_pace[0], 1u);
+          const uint64_t t0 = sm100::globaltimer_ns();
+          while (*reinterpret_cast<volatile unsigned int*>(&g_wave_pace[0]) < target &&
+                 sm100::globaltimer_ns() - t0 < p.pace_ns) {
+          }
+        }
         bool ok = true;
         for (int kc = 0; kc < num_k; ++kc) {
           if (!sm100::mbar_wait(&ctl->empty[ps.stage], ps.phase ^ 1, abort_flag, tmo)) {
@@ -208,6 +226,14 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (warp == 1) {
     sm100::tcgen05_fence_after_sync();
     sm100::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (p.pace_ns != 0 && cta == 0 && threadIdx.x == 0) {
+    // the last pair to finish leaves the pacing counter at zero for the next launch
+    if (atomicAdd(&g_wave_pace[1], 1u) == static_cast<unsigned int>(num_pairs) - 1u) {
+      g_wave_pace[0] = 0u;
+      g_wave_pace[1] = 0u;
+      __threadfence();
+    }
   }
 }
 

@@ -76,6 +76,7 @@ struct TriContractArgs {
   int chan_offset;
   int band_rows;    // tile rows per band of the tile walk (>= 1; 1 = row-major)
   int rot_rows, rot_cols;  // the walk starts at the tile holding this result row / column (this rank's own block)
+  unsigned int pace_ns;    // CTA-pair form: longest time a pair waits for the others before a tile (0 = no pacing)
   unsigned long long* timeline;  // optional device timeline, nullptr = off
   DeviceStatus* status;
   uint64_t timeout_ns;

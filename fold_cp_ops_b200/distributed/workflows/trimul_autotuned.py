@@ -201,7 +201,7 @@ class TriMulAutotuned(TriMulEngine):
     Same constructor shape as the reference's ``TriMulAutotuned(pe_map, B, N, D, w, dt, **kw)``
     (``fold_cp_ops/distributed/workflows/trimul_autotuned.py:2686``).  ``B`` / ``N`` size the
     buffers allocated up front; any other ``N`` meeting the divisibility rules is served later
-    (always dynamic).  ``contract_form``, ``contract_band_rows``, ``contract_fixed_start``, ``front_fixed_order`` and ``wait_timeout_ms`` are the
+    (always dynamic).  ``contract_form``, ``contract_band_rows``, ``contract_fixed_start``, ``contract_pace_ns``, ``front_fixed_order`` and ``wait_timeout_ms`` are the
     sm_100a choices (see :class:`fold_cp_ops_b200.engine.TriMulEngine`); keywords that configured
     SM90 tiles or NVSHMEM drains are accepted and ignored (``trimul_tuning.IGNORED_ON_SM100``)."""
 
@@ -209,7 +209,8 @@ class TriMulAutotuned(TriMulEngine):
                  placements=None, dynamic: bool = True, has_mask: bool = False, eps: float = 1e-5,
                  composite_k: bool = False, route2_ni: bool = False, contract_form: Optional[str] = None,
                  front_fixed_order: Optional[bool] = None, contract_band_rows: Optional[int] = None,
-                 contract_fixed_start: Optional[bool] = None, wait_timeout_ms: Optional[float] = None, front_tile_mn=None, front_pad_inner=None, front_pad_eager=None, back_tile_mn=None,
+                 contract_fixed_start: Optional[bool] = None, contract_pace_ns: Optional[int] = None,
+                 wait_timeout_ms: Optional[float] = None, front_tile_mn=None, front_pad_inner=None, front_pad_eager=None, back_tile_mn=None,
                  back_pingpong=None, back_cluster_n=None, consumer=None, use_device_signal_nvlink=None,
                  autotune_config=None, is_persistent=None, allocate: bool = True):
         if dt is not torch.bfloat16:
@@ -236,7 +237,7 @@ class TriMulAutotuned(TriMulEngine):
         super().__init__(w, device=pe_map.device, eps=eps, geometry=geometry, process_group=group,
                          contract_form=contract_form, front_fixed_order=front_fixed_order,
                          contract_band_rows=contract_band_rows, contract_fixed_start=contract_fixed_start,
-                         wait_timeout_ms=wait_timeout_ms)
+                         contract_pace_ns=contract_pace_ns, wait_timeout_ms=wait_timeout_ms)
         self.pe_map = pe_map
         self.has_mask = bool(has_mask)
         self.composite_k = bool(composite_k)

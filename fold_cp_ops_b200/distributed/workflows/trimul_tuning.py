@@ -66,6 +66,7 @@ class BackTuning:
     contract_form: Optional[str] = _knob("contract_form")
     band_rows: Optional[int] = _knob("contract_band_rows")
     fixed_start: Optional[bool] = _knob("contract_fixed_start")
+    pace_ns: Optional[int] = _knob("contract_pace_ns")
 
 
 @_tuning_group

@@ -108,6 +108,8 @@ class TriMulEngine:
     Tuning (all optional): ``contract_form`` ``"auto" | "single" | "pair"``, ``front_fixed_order``,
     ``contract_band_rows`` (tile rows per band of the contraction's tile walk; 0 = the library's choice),
     ``contract_fixed_start`` (every rank walks the contraction's tiles from tile (0, 0)),
+    ``contract_pace_ns`` (longest wait of a CTA pair for the others before a tile; 0 = the library's choice,
+    negative = off),
     ``wait_timeout_ms`` (bound of the cross-rank flag waits; ``CPO_A2A_WAIT_TIMEOUT_MS`` overrides).
     """
 
@@ -115,7 +117,7 @@ class TriMulEngine:
                  geometry: Optional[CpGeometry] = None, process_group=None, recv_cache: Optional[int] = None,
                  contract_form: Optional[str] = None, front_fixed_order: Optional[bool] = None,
                  contract_band_rows: Optional[int] = None, contract_fixed_start: Optional[bool] = None,
-                 wait_timeout_ms: Optional[float] = None):
+                 contract_pace_ns: Optional[int] = None, wait_timeout_ms: Optional[float] = None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("TriMulEngine needs a CUDA device: the TriMul kernels have no CPU path")
@@ -133,8 +135,9 @@ class TriMulEngine:
         self.front_fixed_order = bool(defaults["front_fixed_order"] if front_fixed_order is None else front_fixed_order)
         self.contract_band_rows = int(defaults.get("contract_band_rows", 0) if contract_band_rows is None else contract_band_rows)
         self.contract_fixed_start = bool(contract_fixed_start)
+        self.contract_pace_ns = int(defaults.get("contract_pace_ns", 0) if contract_pace_ns is None else contract_pace_ns)
         self.tuning = K.make_tuning(self.contract_form, self.front_fixed_order, self.contract_band_rows,
-                                    self.contract_fixed_start)
+                                    self.contract_fixed_start, self.contract_pace_ns)
         self.status = K.new_status(self.device)
         self._status_host = torch.zeros(8, dtype=torch.int32).pin_memory()
         self._status_event: Optional[torch.cuda.Event] = None

@@ -141,12 +141,16 @@ def _ptr_array(ptrs: Sequence[int]):
 
 
 def make_tuning(contract_form: str = "auto", front_fixed_order: bool = False, contract_band_rows: int = 0,
-                contract_fixed_start: bool = False) -> _lib.Tuning:
+                contract_fixed_start: bool = False, contract_pace_ns: int = 0) -> _lib.Tuning:
     """The library's tuning record: ``contract_form`` is ``"auto"`` (CTA pairs whenever the device has two
     SMs), ``"single"`` (one CTA per 128 x 256 tile) or ``"pair"`` (two CTAs per 256 x 256 tile);
     ``contract_band_rows`` is the height, in tile rows, of the bands the contraction walks column by
     column (0: the library's choice, 1: row-major); ``contract_fixed_start`` makes every rank walk from
-    tile (0, 0) instead of from its own block of the result."""
+    tile (0, 0) instead of from its own block of the result; ``contract_pace_ns`` (<= 100000; 0 = the
+    library's choice, negative = off) is the longest a CTA pair waits before a tile for the other pairs to
+    start theirs (a hint that keeps tiles sharing operand strips in step; results never depend on it)."""
+    if int(contract_pace_ns) > 100000:
+        raise ValueError(f"contract_pace_ns must be <= 100000; got {contract_pace_ns}")
     if int(contract_band_rows) < 0:
         raise ValueError(f"contract_band_rows must be >= 0; got {contract_band_rows}")
     forms = {"auto": _lib.CONTRACT_DEFAULT, "single": _lib.CONTRACT_SINGLE, "pair": _lib.CONTRACT_PAIR}
@@ -157,6 +161,7 @@ def make_tuning(contract_form: str = "auto", front_fixed_order: bool = False, co
     t.front_fixed_order = 1 if front_fixed_order else 0
     t.contract_band_rows = int(contract_band_rows)
     t.contract_fixed_start = 1 if contract_fixed_start else 0
+    t.contract_pace_ns = int(contract_pace_ns)
     return t
 
 

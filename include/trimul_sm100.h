@@ -96,7 +96,12 @@ typedef struct trimul_tuning {
   int32_t contract_fixed_start; /* 1: every rank walks the contraction's tiles from tile (0, 0); 0: each rank
                                    starts at the block of the result it owns, so that at cp > 1 the ranks' stores
                                    go to different owners at any moment */
-  int32_t reserved[4];
+  int32_t contract_pace_ns;     /* CTA-pair contraction: before each tile a pair waits at most this long (ns,
+                                   <= 100000) for the other pairs to start theirs, so that tiles that share
+                                   operand strips move through K together and share them in L2.  A hint only:
+                                   no result and no termination depends on it.  0: the library's choice (2000);
+                                   negative: off */
+  int32_t reserved[3];
 } trimul_tuning_t;
 
 /* Optional device timeline of one forward: TRIMUL_TIMELINE_SLOTS x uint64 of %globaltimer (ns) on this

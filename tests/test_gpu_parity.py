@@ -336,23 +336,25 @@ def test_kernel_tri_contract_pair_form_equals_single_cta_form(N):
 def test_kernel_tri_contract_banded_tile_walk_equals_row_major(N, band, form):
     """The order in which the tiles of a plane are walked (bands of `band` tile rows, column by column
     inside a band; bands that do not divide the tile grid included) changes which CTA computes which tile
-    and nothing else: bitwise equal to the row-major walk."""
+    and nothing else, and the pacing of the CTA pairs (off, the library's 2 us, 50 us) only when a pair
+    starts a tile: bitwise equal to the unpaced row-major walk."""
     from fold_cp_ops_b200 import kernels as K
 
     torch.manual_seed(N + band)
     D = 128
     ab = (0.5 * torch.randn(2, D, 1, N, N, device=DEV)).to(torch.bfloat16)
     outs = []
-    for rows in (1, band):
+    for rows, pace in ((1, -1), (band, 0), (band, 50000)):
         tri = torch.full((D, 1, N, N), float("nan"), dtype=torch.bfloat16, device=DEV)
         st = K.new_status(DEV)
         g = K.make_geom(1, N, D, "outgoing", 1e-5)
-        K.tri_contract(g, ab, [tri.data_ptr()], st, tuning=K.make_tuning(form, contract_band_rows=rows))
+        K.tri_contract(g, ab, [tri.data_ptr()], st,
+                       tuning=K.make_tuning(form, contract_band_rows=rows, contract_pace_ns=pace))
         torch.cuda.synchronize()
         K.check_status(st)
         outs.append(tri)
     assert not torch.isnan(outs[0].float()).any()
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
 @pytest.mark.parametrize("D,B,n,offset", [(128, 1, 8, 0.5), (128, 1, 72, 0.5), (256, 2, 40, 0.5), (256, 1, 64, 30.0),

@@ -204,6 +204,10 @@ def test_tuning_surface():
     assert K.make_tuning("pair", contract_band_rows=4).contract_band_rows == 4 and K.make_tuning().contract_band_rows == 0
     with pytest.raises(ValueError, match="contract_band_rows"):
         K.make_tuning(contract_band_rows=-1)
+    assert K.make_tuning(contract_pace_ns=-1).contract_pace_ns == -1 and K.make_tuning().contract_pace_ns == 0
+    with pytest.raises(ValueError, match="contract_pace_ns"):
+        K.make_tuning(contract_pace_ns=200000)
+    assert TriMulTuning(back=BackTuning(pace_ns=5000)).to_engine_kwargs() == {"contract_pace_ns": 5000}
     with pytest.raises(TypeError, match="tile_mm"):
         FrontTuning(tile_mm=(128, 128))
     with pytest.raises(Exception):
