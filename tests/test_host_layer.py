@@ -281,6 +281,49 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, sym), sym
 
 
+def test_ctypes_mirrors_match_the_header_structs(tmp_path):
+    """Every struct of include/trimul_sm100.h, as the C compiler lays it out (field names in order, offsets,
+    total size: a small program compiled here against the header prints them), against its ctypes mirror
+    in `_lib.py`.  A field added on one side only would shift every later field silently."""
+    import re
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    inc = Path(__file__).resolve().parent.parent / "include"
+    header = (inc / "trimul_sm100.h").read_text()
+    mirrors = {"trimul_caps": _lib.Caps, "trimul_geom": _lib.Geom, "trimul_tuning": _lib.Tuning,
+               "trimul_status": _lib.Status, "trimul_plan_desc": _lib.PlanDesc, "trimul_workspace": _lib.Workspace,
+               "trimul_reshard_plan": _lib.ReshardPlan}
+    structs = dict(re.findall(r"typedef struct (\w+) \{(.*?)\} \w+_t;", header, flags=re.S))
+    assert set(structs) == set(mirrors), set(structs) ^ set(mirrors)
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "trimul_sm100.h"', 'int main(void) {']
+    fields = {}
+    for name, body in structs.items():
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = [re.sub(r"\[.*\]", "", d.split()[-1].lstrip("*")) for d in body.split(";") if d.strip()]
+        fields[name] = names
+        lines.append(f'  printf("{name} size %zu\\n", sizeof(struct {name}));')
+        lines += [f'  printf("{name} {f} %zu\\n", offsetof(struct {name}, {f}));' for f in names]
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(inc), str(src), "-o", str(exe)], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    seen = {}
+    for line in filter(None, out):
+        name, field, value = line.split()
+        seen.setdefault(name, {})[field] = int(value)
+    for name, mirror in mirrors.items():
+        assert [f for f, _ in mirror._fields_] == fields[name], (name, fields[name])
+        assert ctypes.sizeof(mirror) == seen[name]["size"], name
+        for f, _ in mirror._fields_:
+            assert getattr(mirror, f).offset == seen[name][f], (name, f)
+
+
 def test_loader_refuses_a_library_built_from_other_sources(monkeypatch):
     """The loader compares the digest compiled into the library with the sources beside it (file times do
     not survive a copy of the tree): the real library matches, a library reporting another digest is stale."""
