@@ -20,14 +20,12 @@ def _is_dtensor(x) -> bool:
 
 def _dtensor_mesh_placements(x):
     """``(device_mesh, placements)`` of a DTensor, with the ``_spec`` fallback."""
-    mesh = getattr(x, "device_mesh", None)
-    placements = getattr(x, "placements", None)
     spec = getattr(x, "_spec", None)
-    if mesh is None and spec is not None:
-        mesh = spec.mesh
-    if placements is None and spec is not None:
-        placements = spec.placements
-    return mesh, tuple(placements)
+    found = []
+    for own, from_spec in (("device_mesh", "mesh"), ("placements", "placements")):
+        value = getattr(x, own, None)
+        found.append(getattr(spec, from_spec) if value is None and spec is not None else value)
+    return found[0], tuple(found[1])
 
 
 def _rowmaj_stride(shape: Sequence[int]) -> Tuple[int, ...]:
@@ -38,35 +36,41 @@ def _rowmaj_stride(shape: Sequence[int]) -> Tuple[int, ...]:
     return tuple(reversed(stride))
 
 
+def _shards(placements: Sequence):
+    """``(mesh axis, tensor dim)`` of every ``Shard`` placement, in mesh-axis order."""
+    return [(axis, _placement_shard_dim(p)) for axis, p in enumerate(placements) if _is_shard(p)]
+
+
+def _split_of_tensor_dim(device_mesh, placements: Sequence, tensor_dim: int) -> int:
+    """How many ways the mesh splits ``tensor_dim`` (product of the sizes of the axes that shard it)."""
+    sizes = tuple(device_mesh.mesh.shape)
+    ways = 1
+    for axis, dim in _shards(placements):
+        if dim == tensor_dim:
+            ways *= int(sizes[axis])
+    return ways
+
+
 def validate_trimul_sharding(placements: Sequence, ndim_mesh: int) -> Tuple[int, ...]:
     """Return the mesh dims that shard a token axis; raise ``ValueError`` on an unusable sharding."""
     if len(placements) != ndim_mesh:
         raise ValueError(f"placements length {len(placements)} != mesh ndim {ndim_mesh}")
-    sharded_dims, cp_axes = [], []
-    for axis, p in enumerate(placements):
-        if _is_shard(p):
-            tdim = _placement_shard_dim(p)
-            sharded_dims.append(tdim)
-            if tdim in _TOKEN_TENSOR_DIMS:
-                cp_axes.append(axis)
-    if 3 in sharded_dims:
+    shards = _shards(placements)
+    if any(dim == 3 for _, dim in shards):
         raise ValueError("TriMul requires the feature dim (3) to be UN-sharded (LN + DualGatedGEMM reduce over "
                          f"full D), but placements {placements} shard tensor dim 3.")
-    if not cp_axes:
+    token_axes = tuple(axis for axis, dim in shards if dim in _TOKEN_TENSOR_DIMS)
+    if not token_axes:
         raise ValueError("TriMul requires at least one token axis (tensor dim 1 or 2) to be sharded over the cp "
                          f"mesh, but placements {placements} shard none. Expected the "
                          "(Shard(0),Shard(1),Shard(2)) pattern.")
-    return tuple(cp_axes)
+    return token_axes
 
 
 def _token_split_factor(device_mesh, placements: Sequence) -> int:
     """Product of the mesh-axis sizes that split a token axis; 1 means the contraction is local."""
-    shape = tuple(device_mesh.mesh.shape)
-    factor = 1
-    for axis, p in enumerate(placements):
-        if _is_shard(p) and _placement_shard_dim(p) in _TOKEN_TENSOR_DIMS:
-            factor *= int(shape[axis])
-    return factor
+    rows, cols = (_split_of_tensor_dim(device_mesh, placements, dim) for dim in _TOKEN_TENSOR_DIMS)
+    return rows * cols
 
 
 def _effective_placements(device_mesh, placements: Sequence) -> list:
@@ -91,13 +95,5 @@ def _ensure_nvshmem(distributed_manager=None) -> None:
 def _is_rows_sharded_canonical(device_mesh, placements: Sequence) -> bool:
     """True when the ONLY token axis split over the mesh is the row axis (tensor dim 1): the
     canonical 1-D layout ``(dp=1, cp0=cp, cp1=1)``."""
-    shape = tuple(device_mesh.mesh.shape)
-    rows = cols = 1
-    for axis, p in enumerate(placements):
-        if _is_shard(p):
-            d = _placement_shard_dim(p)
-            if d == 1:
-                rows *= int(shape[axis])
-            elif d == 2:
-                cols *= int(shape[axis])
+    rows, cols = (_split_of_tensor_dim(device_mesh, placements, dim) for dim in _TOKEN_TENSOR_DIMS)
     return rows > 1 and cols == 1
