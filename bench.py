@@ -538,12 +538,12 @@ def run_ours(args):
         peaks = measured_peaks()
         fl = flops(B, N, D)
         tf = fl / (ms * 1e-3) / 1e12
-        # dominant kernel: the contraction; algorithmic FLOPs per launch = 2*B*(D/cp)*N^3 on each rank
-        fl_b = 2.0 * B * (D / cp) * N ** 3
-        # one launch contracts planes_b batch planes of this rank's D/cp channels (planes_b = B unless the
-        # workspace was capped to one batch plane per launch)
+        # dominant kernel: the contraction.  One launch contracts planes_b batch planes of this rank's D/cp
+        # channels (planes_b = B unless the workspace was capped to one batch plane per launch); the stage
+        # windows time ONE launch, so the algorithmic FLOPs beside them are those of one launch
         planes_b = getattr(next(iter(eng._ws.values())), "planes_b", B) if eng is not None and eng._ws else B
         planes_per_launch = planes_b * (D // cp)
+        fl_b = 2.0 * planes_per_launch * N ** 3
         ach = fl_b / (t_b * 1e-3) / 1e12 if t_b > 0 else None
         peak = peaks["bf16_tflops_sustained"]
         roof = {"bound": "tensor", "kernel": "tri_contract_pair_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
@@ -557,7 +557,8 @@ def run_ours(args):
                 "frac_of_burst_peak": (ach / peaks["bf16_tflops"]) if ach else None,
                 "stage_ms": {"ln_gated_proj": t_a, "tri_contract": t_b, "ln_out_proj": t_c},
                 "stage_ms_note": "CUDA events around each kernel alone (max over ranks); the flag kernels between "
-                                 "them are outside these windows"}
+                                 "them are outside these windows",
+                "launches_per_kernel_per_step": B // planes_b}
         # whole-step roofline: the slowest of tensor time, HBM time (9 S per rank) and NVLink egress (3 S (cp-1)/cp)
         S = B * N * N * D * 2.0 / cp
         t_tc = fl / cp / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3

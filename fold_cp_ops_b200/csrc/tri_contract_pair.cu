@@ -45,8 +45,8 @@ constexpr int kSmemBytes = kStages * kStageBytes + tri::kOutStageBytes + 1024 /*
 // Wave pacing (a performance hint, never a dependency).  Tiles that run at the same time share operand
 // strips through L2 only while they move through K together; left alone, the pairs drift apart by a good
 // part of a tile and most of that sharing is lost.  Before loading its n-th tile a pair's first producer
-// counts itself in and waits -- for at most `pace_ns`, a time the six loaded stages cover -- until the other
-// pairs have started their n-th tile too.  A pair that is late never waits, an early pair gives up after
+// counts itself in and waits -- for at most `pace_ns` -- until the other pairs have started their n-th tile
+// too (while the pairs are in step that wait is far shorter than the six loaded stages cover).  A pair that is late never waits, an early pair gives up after
 // pace_ns and loads anyway, so no result and no termination depends on the counter; the last pair out resets
 // it.  [0]: tiles started, [1]: pairs finished.
 __device__ unsigned int g_wave_pace[2];

@@ -99,7 +99,7 @@ typedef struct trimul_tuning {
   int32_t contract_pace_ns;     /* CTA-pair contraction: before each tile a pair waits at most this long (ns,
                                    <= 100000) for the other pairs to start theirs, so that tiles that share
                                    operand strips move through K together and share them in L2.  A hint only:
-                                   no result and no termination depends on it.  0: the library's choice (2000);
+                                   no result and no termination depends on it.  0: the library's choice (20000);
                                    negative: off */
   int32_t reserved[3];
 } trimul_tuning_t;

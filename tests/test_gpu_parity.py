@@ -336,7 +336,7 @@ def test_kernel_tri_contract_pair_form_equals_single_cta_form(N):
 def test_kernel_tri_contract_banded_tile_walk_equals_row_major(N, band, form):
     """The order in which the tiles of a plane are walked (bands of `band` tile rows, column by column
     inside a band; bands that do not divide the tile grid included) changes which CTA computes which tile
-    and nothing else; the pacing of the CTA pairs (off, the library's 2 us, 50 us) changes only WHEN a pair
+    and nothing else; the pacing of the CTA pairs (off, the library's 20 us, 50 us) changes only WHEN a pair
     starts a tile.  Every combination is bitwise equal to the unpaced row-major walk."""
     from fold_cp_ops_b200 import kernels as K
 
