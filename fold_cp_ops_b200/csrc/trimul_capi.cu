@@ -348,12 +348,12 @@ int launch_front(FrontPart& part, const void* x, const void* mask, int32_t mask_
 // 86.9 GB, bands of 4 / 8 / 16 rows 61.8 / 58.8 / 63.2 GB (first touch is 17.2 GB); the kernel's time is the
 // same within the run-to-run spread, so the choice is the one that moves the fewest bytes.
 constexpr int kDefaultBandRows = 8;
-// Longest wait of a CTA pair for the other pairs before a tile.  Measured inside full forwards, alternating in one
-// process.  n = 8192, 128 planes (a tile streams 8 MB; unpaced, the pairs' re-reads ask more of DRAM than it has):
-// unpaced 138-145 ms, 2 us 120 ms (single forwards 97-141), 5 us 106, 20 us 102 (97-110), 60 us 104.  n = 4096,
-// 256 planes: unpaced 25.3 ms, 2 / 5 / 20 us 25.6 / 25.6 / 24.8; DRAM reads 58.8 GB unpaced, 48.1 GB paced (2 us
-// and 20 us alike).  A bound of a few us pulls a pair that has drifted back by only that much per tile; 20 us
-// (most of a tile) re-locks it at once.
+// Longest wait of a CTA pair for the other pairs before a tile.  Alternating bounds inside full forwards in one
+// process at n = 8192, 128 planes (a tile streams 8 MB; unpaced, the pairs' re-reads can ask more of DRAM than it
+// has): unpaced 138-145 ms, 2 us 120 ms (single forwards 97-141), 5 us 106, 20 us 102 (97-110), 60 us 104; runs of
+// one bound per process on other devices read 99-106 ms with and without pacing.  n = 4096, 256 planes: unpaced
+// 25.3 ms, 2 / 5 / 20 us 25.6 / 25.6 / 24.8; DRAM reads 58.8 GB unpaced, 48.1 GB paced.  A bound of a few us pulls
+// a pair that has drifted back by only that much per tile; 20 us re-locks it at once.
 constexpr int kDefaultPaceNs = 20000;
 
 int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tuning_t* tuning, const void* ab_local,
