@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "trimul_sm100_query",
     "trimul_sm100_workspace",
     "trimul_sm100_reshard_plan",
+    "trimul_sm100_contract_walk",
     "trimul_sm100_last_error",
     "trimul_sm100_build_id",
     "trimul_sm100_pack_weights",
@@ -155,6 +156,9 @@ def load():
         lib.trimul_sm100_workspace.argtypes = [C.POINTER(Geom), C.POINTER(Workspace)]
         lib.trimul_sm100_reshard_plan.argtypes = [C.POINTER(Geom), C.POINTER(ReshardPlan)]
         lib.trimul_sm100_reshard_plan.restype = C.c_int
+        lib.trimul_sm100_contract_walk.argtypes = [C.POINTER(Geom), C.POINTER(Tuning), C.c_int32, C.POINTER(C.c_int32),
+                                                   C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+        lib.trimul_sm100_contract_walk.restype = C.c_int
         lib.trimul_sm100_pack_weights.argtypes = [i32, vp, vp, vp, f32p, f32p, f32p, vp, f32p, vp]
         lib.trimul_sm100_ln_gated_proj.argtypes = [C.POINTER(Geom), C.POINTER(Tuning), vp, vp, i32, f32p, f32p, vp, f32p,
                                                    C.POINTER(vp), vp, vp, u64, vp]

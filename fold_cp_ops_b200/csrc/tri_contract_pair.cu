@@ -240,6 +240,20 @@ tri_contract_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
+// The walk the kernel above makes over one plane's tile grid, evaluated on the host (same tile sizes, same
+// arithmetic): position r of the walk is tile (ti[r], tj[r]).
+void tri_contract_pair_walk(const TriContractArgs& args, int capacity, int* ti, int* tj, int* tiles_i_out,
+                            int* tiles_j_out) {
+  const int tiles_i = (args.n_i + 2 * BM - 1) / (2 * BM);
+  const int tiles_j = (args.n_j + BN - 1) / BN;
+  const int rot_i = (args.rot_rows / (2 * BM)) % tiles_i;
+  const int rot_j = (args.rot_cols / BN) % tiles_j;
+  *tiles_i_out = tiles_i;
+  *tiles_j_out = tiles_j;
+  for (int r = 0; r < tiles_i * tiles_j && r < capacity; ++r)
+    tile_of(r, tiles_i, tiles_j, args.band_rows, rot_i, rot_j, ti[r], tj[r]);
+}
+
 cudaError_t launch_tri_contract_pair(const CUtensorMap& tmA, const CUtensorMap& tmBhalf, const TriOutMaps& out_maps,
                                      const TriContractArgs& args, int num_sms, cudaStream_t stream) {
   cudaError_t e =

@@ -356,6 +356,22 @@ constexpr int kDefaultBandRows = 8;
 // a pair that has drifted back by only that much per tile; 20 us re-locks it at once.
 constexpr int kDefaultPaceNs = 20000;
 
+// How the contraction walks a plane's tiles, from the tuning record: band height, where the walk starts, pacing.
+int derive_walk(const Derived& d, const trimul_tuning_t* tuning, trimul::TriContractArgs* a) {
+  const int band = tuning != nullptr ? tuning->contract_band_rows : 0;
+  if (band < 0) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_band_rows=%d must be >= 0", band);
+  a->band_rows = band > 0 ? band : kDefaultBandRows;
+  const int pace = tuning != nullptr ? tuning->contract_pace_ns : 0;
+  if (pace > 100000) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_pace_ns=%d must be <= 100000", pace);
+  a->pace_ns = pace < 0 ? 0u : static_cast<unsigned int>(pace > 0 ? pace : kDefaultPaceNs);
+  // every rank starts its walk at the block of the result it owns itself and all ranks advance alike, so at any
+  // moment the ranks' stores go to different owners (a rotation of the ranks) instead of all to the same one
+  const bool fixed_start = tuning != nullptr && tuning->contract_fixed_start != 0;
+  a->rot_rows = fixed_start ? 0 : static_cast<int>(d.i_off);
+  a->rot_cols = fixed_start ? 0 : static_cast<int>(d.j_off);
+  return TRIMUL_OK;
+}
+
 int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tuning_t* tuning, const void* ab_local,
                    void* const* tri_peers, trimul_status_t* status, uint64_t* timeline, uint64_t timeout_ns, int num_sms,
                    ContractPart* out) {
@@ -394,17 +410,10 @@ int build_contract(const trimul_geom_t* geom, const Derived& d, const trimul_tun
   a.nj_loc = d.nj_loc;
   a.cp1 = geom->cp1;
   a.chan_offset = geom->rank * d.d_loc;
-  const int band = tuning != nullptr ? tuning->contract_band_rows : 0;
-  if (band < 0) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_band_rows=%d must be >= 0", band);
-  a.band_rows = band > 0 ? band : kDefaultBandRows;
-  // every rank starts its walk at the block of the result it owns itself and all ranks advance alike, so at any
-  // moment the ranks' stores go to different owners (a rotation of the ranks) instead of all to the same one
-  const int pace = tuning != nullptr ? tuning->contract_pace_ns : 0;
-  if (pace > 100000) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_pace_ns=%d must be <= 100000", pace);
-  a.pace_ns = pace < 0 ? 0u : static_cast<unsigned int>(pace > 0 ? pace : kDefaultPaceNs);
-  const bool fixed_start = tuning != nullptr && tuning->contract_fixed_start != 0;
-  a.rot_rows = fixed_start ? 0 : static_cast<int>(d.i_off);
-  a.rot_cols = fixed_start ? 0 : static_cast<int>(d.j_off);
+  {
+    int rc = derive_walk(d, tuning, &a);
+    if (rc != TRIMUL_OK) return rc;
+  }
   memset(&out->maps, 0, sizeof(out->maps));
   {
     // every owner's tri buffer as (columns, rows, channel planes of ALL D channels x batch)
@@ -546,6 +555,32 @@ int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* 
   if (rc != TRIMUL_OK) return rc;
   if (out == nullptr) return fail(TRIMUL_ERR_INVALID_ARGUMENT, "plan is NULL");
   derive_plan(geom, d, out);
+  return TRIMUL_OK;
+}
+
+int trimul_sm100_contract_walk(const trimul_geom_t* geom, const trimul_tuning_t* tuning, int32_t capacity,
+                               int32_t* tile_row, int32_t* tile_col, int32_t* tiles_i, int32_t* tiles_j) {
+  Derived d;
+  int rc = check_geom(geom, &d);
+  if (rc != TRIMUL_OK) return rc;
+  if (!tiles_i || !tiles_j || capacity < 0 || (capacity > 0 && (!tile_row || !tile_col)))
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "contract_walk: NULL output or negative capacity");
+  const int form = tuning != nullptr ? tuning->contract_form : TRIMUL_CONTRACT_DEFAULT;
+  if (form < TRIMUL_CONTRACT_DEFAULT || form > TRIMUL_CONTRACT_PAIR)
+    return fail(TRIMUL_ERR_INVALID_ARGUMENT, "tuning.contract_form=%d is not one of TRIMUL_CONTRACT_*", form);
+  trimul::TriContractArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n_i = a.n_j = a.n_k = geom->n;
+  rc = derive_walk(d, tuning, &a);
+  if (rc != TRIMUL_OK) return rc;
+  int ti = 0, tj = 0;
+  if (form == TRIMUL_CONTRACT_SINGLE) {
+    trimul::tri_contract_walk(a, capacity, tile_row, tile_col, &ti, &tj);
+  } else {
+    trimul::tri_contract_pair_walk(a, capacity, tile_row, tile_col, &ti, &tj);
+  }
+  *tiles_i = ti;
+  *tiles_j = tj;
   return TRIMUL_OK;
 }
 

@@ -65,12 +65,13 @@ __device__ __forceinline__ void timeline_max(unsigned long long* tl, int slot) {
 // `rot_i` / `rot_j` shift where the walk starts (in tiles, modulo the grid): at cp > 1 every rank starts at the
 // tiles whose result it owns itself, so that at any moment the ranks' stores go to different owners instead of
 // all to the owner of the first rows.
-__device__ __forceinline__ void tile_of(int r, int tiles_i, int tiles_j, int band_rows, int rot_i, int rot_j, int& ti,
-                                        int& tj) {
+__host__ __device__ __forceinline__ void tile_of(int r, int tiles_i, int tiles_j, int band_rows, int rot_i, int rot_j,
+                                                 int& ti, int& tj) {
   const int band_tiles = band_rows * tiles_j;
   const int band = r / band_tiles;
   const int rem = r - band * band_tiles;
-  const int rows = min(band_rows, tiles_i - band * band_rows);
+  const int left = tiles_i - band * band_rows;
+  const int rows = band_rows < left ? band_rows : left;
   tj = rem / rows;
   ti = band * band_rows + (rem - tj * rows) + rot_i;
   tj += rot_j;

@@ -91,6 +91,10 @@ int tri_contract_smem_bytes();
 cudaError_t launch_tri_contract(const CUtensorMap& tmA, const CUtensorMap& tmB, const TriOutMaps& out_maps,
                                 const TriContractArgs& args, int num_sms, cudaStream_t stream);
 
+// host-side evaluation of the kernels' tile walk over one plane (position r -> tile (ti[r], tj[r]))
+void tri_contract_walk(const TriContractArgs& args, int capacity, int* ti, int* tj, int* tiles_i, int* tiles_j);
+void tri_contract_pair_walk(const TriContractArgs& args, int capacity, int* ti, int* tj, int* tiles_i, int* tiles_j);
+
 // CTA-pair form (tcgen05 cta_group::2, 256 x 256 tile per pair); tmBhalf has box (64, 128, 1)
 cudaError_t launch_tri_contract_pair(const CUtensorMap& tmA, const CUtensorMap& tmBhalf, const TriOutMaps& out_maps,
                                      const TriContractArgs& args, int num_sms, cudaStream_t stream);

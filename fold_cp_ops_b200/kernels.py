@@ -68,6 +68,21 @@ def reshard_plan(geom: _lib.Geom) -> _lib.ReshardPlan:
     return plan
 
 
+def contract_walk(geom: _lib.Geom, tuning: Optional[_lib.Tuning] = None):
+    """``((tiles_i, tiles_j), [(tile_row, tile_col), ...])``: the order in which the contraction kernel visits
+    the tiles of one channel plane for this rank and tuning (host-side; no device work)."""
+    lib = _lib.load()
+    ti, tj = C.c_int32(0), C.c_int32(0)
+    ref = None if tuning is None else C.byref(tuning)
+    _lib.check(lib.trimul_sm100_contract_walk(C.byref(geom), ref, 0, None, None, C.byref(ti), C.byref(tj)),
+               "trimul_sm100_contract_walk")
+    n = ti.value * tj.value
+    rows, cols = (C.c_int32 * n)(), (C.c_int32 * n)()
+    _lib.check(lib.trimul_sm100_contract_walk(C.byref(geom), ref, n, rows, cols, C.byref(ti), C.byref(tj)),
+               "trimul_sm100_contract_walk")
+    return (ti.value, tj.value), list(zip(rows, cols))
+
+
 def new_status(device) -> torch.Tensor:
     """A zeroed device status record (8 x int32) for the bounded waits to report into."""
     return torch.zeros(8, dtype=torch.int32, device=device)

@@ -158,6 +158,14 @@ typedef struct trimul_reshard_plan {
 int trimul_sm100_query(int device, trimul_caps_t* out);
 int trimul_sm100_reshard_plan(const trimul_geom_t* geom, trimul_reshard_plan_t* out);
 int trimul_sm100_workspace(const trimul_geom_t* geom, trimul_workspace_t* out);
+/* Host-only: the order in which the contraction kernel visits the tiles of one channel plane for this rank and
+ * tuning (tuning->contract_form picks the tile height: 256 rows for CTA pairs -- also the default -- 128 for the
+ * single-CTA form; tiles are 256 columns wide).  Writes the grid size to tiles_i / tiles_j and, for the first
+ * min(capacity, tiles_i*tiles_j) positions r of the walk, the tile's row and column index to tile_row[r] /
+ * tile_col[r].  Evaluates the same function the kernels call; touches no device.  Takes over what the reference
+ * leaves to its persistent tile scheduler (fold_cp_ops/distributed/gemm_a2a_epi.py:78). */
+int trimul_sm100_contract_walk(const trimul_geom_t* geom, const trimul_tuning_t* tuning /* nullable */, int32_t capacity,
+                               int32_t* tile_row, int32_t* tile_col, int32_t* tiles_i, int32_t* tiles_j);
 const char* trimul_sm100_last_error(void);
 /* Digest of the sources this library was compiled from (set by the build script; "unknown" for a hand
  * build).  The Python loader compares it with the sources beside the library and refuses a stale one.

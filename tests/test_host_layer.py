@@ -281,6 +281,43 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, sym), sym
 
 
+@pytest.mark.parametrize("form,tile_rows", [("pair", 256), ("single", 128)])
+def test_contraction_tile_walk_is_a_permutation_and_rotates_the_owners(form, tile_rows):
+    """`trimul_sm100_contract_walk` evaluates, on the host, the function the contraction kernels use to pick
+    their next tile.  Whatever the band height, grid shape, rank and start rule, every tile of a plane is visited
+    exactly once; a band is walked column by column; every rank starts in its own block of the result; and
+    at any position of the walk the ranks of a 1-D grid are in the row blocks of DIFFERENT owners."""
+    from fold_cp_ops_b200 import kernels as K
+
+    for N, cp0, cp1 in ((8, 1, 1), (600, 1, 1), (1280, 1, 1), (4096, 1, 1), (4096, 4, 1), (4096, 2, 4), (1536, 2, 2)):
+        for band in (0, 1, 3, 8, 64):
+            for rank in range(cp0 * cp1):
+                for fixed in (False, True):
+                    g = K.make_geom(1, N, 128, "incoming", 1e-5, cp0, cp1, rank)
+                    t = K.make_tuning(form, contract_band_rows=band, contract_fixed_start=fixed)
+                    (ti, tj), walk = K.contract_walk(g, t)
+                    assert (ti, tj) == (-(-N // tile_rows), -(-N // 256))
+                    assert sorted(walk) == [(i, j) for i in range(ti) for j in range(tj)], (N, cp0, cp1, band, rank)
+                    r0, r1 = rank // cp1, rank % cp1
+                    start = (0, 0) if fixed else ((r0 * (N // cp0)) // tile_rows % ti, (r1 * (N // cp1)) // 256 % tj)
+                    assert walk[0] == start
+                    rows = min(band or 8, ti)
+                    assert len({c for _, c in walk[:rows]}) == 1 and len({r for r, _ in walk[:rows]}) == rows
+    # a NULL tuning is the library's default: CTA pairs, bands of 8, own-block start
+    g = K.make_geom(1, 4096, 256, "outgoing", 1e-5, 8, 1, 3)
+    assert K.contract_walk(g) == K.contract_walk(g, K.make_tuning("pair", contract_band_rows=8))
+    # the rotation: at every position the eight ranks store into eight different owners' row blocks
+    walks = [K.contract_walk(K.make_geom(1, 4096, 256, "outgoing", 1e-5, 8, 1, r), K.make_tuning(form))[1]
+             for r in range(8)]
+    for pos in range(len(walks[0])):
+        owners = {w[pos][0] * tile_rows // 512 for w in walks}
+        assert len(owners) == 8, (pos, owners)
+    with pytest.raises(Exception, match="contract_band_rows"):
+        bad = K.make_tuning(form)
+        bad.contract_band_rows = -2
+        K.contract_walk(g, bad)
+
+
 def test_ctypes_mirrors_match_the_header_structs(tmp_path):
     """Every struct of include/trimul_sm100.h, as the C compiler lays it out (field names in order, offsets,
     total size: a small program compiled here against the header prints them), against its ctypes mirror
