@@ -42,6 +42,9 @@ DEFAULT_PEER_TIMEOUT_NS = 30_000_000_000
 #: whether the projection kernel's CTAs walk their gated chunks in rotated order.  CTA pairs won at
 #: every shape (27.5 vs 30.8 ms at N=4096 D=256, 3.13 vs 3.45 ms at N=2048); the rotation costs nothing
 #: at cp=1 and spreads the peer stores over all NVLink directions at cp>1 (cp=2: 9.1-9.4 vs 9.7-10.3 ms).
+#: The contraction's tile walk (bands of 8 tile rows, own-block start) and the pacing of its CTA pairs (20 us)
+#: are the library's own defaults (a zero in the tuning record); an entry here may override them per (D, cp)
+#: with "contract_band_rows" / "contract_pace_ns".
 SM100_DEFAULTS = {(d, cp): {"contract_form": "pair", "front_fixed_order": False}
                   for d in SUPPORTED_D for cp in (1, 2, 4, 8)}
 
